@@ -1,0 +1,150 @@
+// Embedding gather, residual-add + RMSNorm, SwiGLU and casts.
+//
+// The residual stream is float32 in every mode; norms reduce in float32 in an
+// order fixed by the row width alone, so a row's result does not depend on
+// what else is in the batch.  Formulas: src/model/native.rs:213-229 (gather),
+// src/model/math.rs:28-50 (RMSNorm), src/model/math.rs:11-22 (SiLU).
+#include "common.cuh"
+
+namespace srlm {
+
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                    float* __restrict__ out, int H, int vocab, int* __restrict__ bad) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (id < 0 || id >= vocab) {          // the host checks too; never read outside the table
+    if (threadIdx.x == 0) atomicExch(bad, 1);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = to_float(row[i]);
+}
+
+// x = residual[src] (+ delta[src]); residual[src] = x when rows == nullptr;
+// out[r] = x * rsqrt(mean(x^2) + eps) * (w (+1)).
+template <typename TA>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                                   const float* __restrict__ weight, float eps, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int H, int unit_offset) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* res = residual + src * H;
+  const TA* del = delta ? delta + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float x = res[i];
+    if (del) {
+      x += to_float(del[i]);
+      if (!rows) res[i] = x;
+    }
+    ss += x * x;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  TA* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float x = res[i];
+    if (del && rows) x += to_float(del[i]);
+    const float w = weight[i] + (unit_offset ? 1.f : 0.f);
+    o[i] = from_float<TA>(x * inv * w);
+  }
+}
+
+__device__ __forceinline__ float silu_f(float x) {
+  // branch-stable logistic, src/model/math.rs:11-22
+  if (x >= 0.f) return x / (1.f + expf(-x));
+  const float e = expf(x);
+  return x * (e / (1.f + e));
+}
+
+// in[T, 2I]: gate in columns [0, I), up in [I, 2I)  ->  out[T, I]
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ in, TA* __restrict__ out, int I, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I, i = idx % I;
+    const float g = to_float(in[t * 2 * I + i]);
+    const float u = to_float(in[t * 2 * I + I + i]);
+    out[idx] = from_float<TA>(silu_f(g) * u);
+  }
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_float<TO>(to_float(in[i]));
+}
+
+// out[t] += delta[t]  (float32 residual, any activation type)
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ residual, const TA* __restrict__ delta, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    residual[i] += to_float(delta[i]);
+}
+
+static inline int norm_block(int H) {
+  int b = 32;
+  while (b < 1024 && b * 4 < H) b <<= 1;
+  return b;
+}
+static inline int flat_grid(size_t n, int block) {
+  size_t g = (n + block - 1) / block;
+  return (int)(g > 148 * 16 ? 148 * 16 : (g == 0 ? 1 : g));
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+extern "C" int srlm_embed_gather(const int* ids, const void* table, int table_dtype, float* out, int T,
+                                 int H, int vocab, int* bad_flag, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (H <= 0 || vocab <= 0) return refuse(ST_BAD_SIZE, "embed_gather: H=%d vocab=%d", H, vocab);
+  const int block = H >= 1024 ? 256 : 128;
+  SRLM_DISPATCH_ACT(table_dtype, TW, (embed_gather_kernel<TW><<<T, block, 0, stream>>>(
+      ids, (const TW*)table, out, H, vocab, bad_flag)));
+  return launched();
+}
+
+extern "C" int srlm_add_rmsnorm(float* residual, const void* delta, const float* weight, float eps,
+                                void* out, int act_dtype, const int* rows, int R, int H, int unit_offset,
+                                cudaStream_t stream) {
+  if (R <= 0) return ST_OK;
+  if (H <= 0 || !(eps > 0.f)) return refuse(ST_BAD_SIZE, "add_rmsnorm: H=%d eps=%g", H, (double)eps);
+  SRLM_DISPATCH_ACT(act_dtype, TA, (add_rmsnorm_kernel<TA><<<R, norm_block(H), 0, stream>>>(
+      residual, (const TA*)delta, weight, eps, (TA*)out, rows, H, unit_offset)));
+  return launched();
+}
+
+extern "C" int srlm_swiglu(const void* in, void* out, int act_dtype, int T, int I, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (I <= 0) return refuse(ST_BAD_SIZE, "swiglu: I=%d", I);
+  const size_t total = (size_t)T * I;
+  SRLM_DISPATCH_ACT(act_dtype, TA, (swiglu_kernel<TA><<<flat_grid(total, 256), 256, 0, stream>>>(
+      (const TA*)in, (TA*)out, I, total)));
+  return launched();
+}
+
+extern "C" int srlm_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                         cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  const int grid = flat_grid((size_t)n, 256);
+  if (in_dtype == DT_F32 && out_dtype == DT_BF16)
+    cast_kernel<float, bf16><<<grid, 256, 0, stream>>>((const float*)in, (bf16*)out, (size_t)n);
+  else if (in_dtype == DT_BF16 && out_dtype == DT_F32)
+    cast_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
+  else
+    return refuse(ST_BAD_DTYPE, "cast: %d -> %d is not offered", in_dtype, out_dtype);
+  return launched();
+}
+
+extern "C" int srlm_residual_add(float* residual, const void* delta, int act_dtype, long long n,
+                                 cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  SRLM_DISPATCH_ACT(act_dtype, TA, (residual_add_kernel<TA><<<flat_grid((size_t)n, 256), 256, 0, stream>>>(
+      residual, (const TA*)delta, (size_t)n)));
+  return launched();
+}

@@ -1,0 +1,116 @@
+// Rotation table, and the fused per-head RMSNorm of q and k + rotary encoding +
+// append of k and v to the paged cache.
+//
+// Formulas: per-head norm src/model/native.rs:629-634, rotation
+// src/model/math.rs:52-99 (half-split pairs (i, i+half), angle =
+// pos / theta^(2i/rotary_dim)), append before attending src/model/native.rs:637.
+// The angle is formed in double precision and rounded once, so cos and sin are
+// exact to float32 at every position.
+#include "common.cuh"
+
+namespace srlm {
+
+__global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cos_out,
+                                  float* __restrict__ sin_out, int T, int half, double theta,
+                                  int rotary_dim) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  const int t = idx / half, i = idx % half;
+  const double angle = (double)positions[t] / pow(theta, (2.0 * i) / (double)rotary_dim);
+  double s, c;
+  sincos(angle, &s, &c);
+  cos_out[idx] = (float)c;
+  sin_out[idx] = (float)s;
+}
+
+// One warp per (token, head) of the fused projection output
+// qkv[T, (nq + 2 nkv) * hd]: heads [0,nq) are queries, [nq, nq+nkv) keys, then values.
+// kv_slot[t] = page * page_size + offset of token t in this cache group, or -1 to skip the append.
+template <typename TA, typename TC>
+__global__ void qk_norm_rope_append_kernel(
+    const TA* __restrict__ qkv, TA* __restrict__ q_out, TC* __restrict__ k_cache,
+    TC* __restrict__ v_cache, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+    float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    const int* __restrict__ kv_slot, int T, int nq, int nkv, int hd, int rotary_half,
+    int heads_total, int write_kv) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T * heads_total) return;
+  const int t = warp / heads_total, head = warp % heads_total;
+  const int width = (nq + 2 * nkv) * hd;
+  const TA* src = qkv + (size_t)t * width + (size_t)head * hd;
+  const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+  if (!is_q && !write_kv) return;
+  const int slot = is_q ? 0 : kv_slot[t];
+  if (!is_q && slot < 0) return;
+
+  if (!is_q && !is_k) {   // value: copy
+    TC* dst = v_cache + ((size_t)slot * nkv + (head - nq - nkv)) * hd;
+    for (int d = lane; d < hd; d += 32) dst[d] = from_float<TC>(to_float(src[d]));
+    return;
+  }
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) { const float x = to_float(src[d]); ss += x * x; }
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  TA* qdst = is_q ? q_out + ((size_t)t * nq + head) * hd : nullptr;
+  TC* kdst = is_k ? k_cache + ((size_t)slot * nkv + (head - nq)) * hd : nullptr;
+  auto put = [&](int d, float v) {
+    if (is_q) qdst[d] = from_float<TA>(v); else kdst[d] = from_float<TC>(v);
+  };
+  auto get = [&](int d) {
+    const float x = to_float(src[d]);
+    return w ? x * inv * w[d] : x;
+  };
+  const float* cs = cos_t + (size_t)t * rotary_half;
+  const float* sn = sin_t + (size_t)t * rotary_half;
+  for (int i = lane; i < rotary_half; i += 32) {
+    const float l = get(i), r = get(i + rotary_half);
+    const float c = cs[i], s = sn[i];
+    put(i, l * c - r * s);
+    put(i + rotary_half, r * c + l * s);
+  }
+  for (int d = 2 * rotary_half + lane; d < hd; d += 32) put(d, get(d));   // unrotated tail
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+extern "C" int srlm_rope_table(const int* positions, float* cos_out, float* sin_out, int T, int half,
+                               double theta, int rotary_dim, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (half <= 0 || rotary_dim != 2 * half || !(theta > 0.0))
+    return refuse(ST_BAD_SIZE, "rope_table: rotary_dim=%d half=%d theta=%g", rotary_dim, half, theta);
+  const int n = T * half;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, cos_out, sin_out, T, half, theta,
+                                                        rotary_dim);
+  return launched();
+}
+
+extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dtype, void* k_cache,
+                                        void* v_cache, int cache_dtype, const float* q_norm_w,
+                                        const float* k_norm_w, float eps, const float* cos_t,
+                                        const float* sin_t, const int* kv_slot, int T, int nq,
+                                        int nkv, int hd, int rotary_half, int write_kv,
+                                        cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (nq <= 0 || nkv <= 0 || hd <= 0 || rotary_half < 0 || 2 * rotary_half > hd)
+    return refuse(ST_BAD_SIZE, "qk_norm_rope_append: nq=%d nkv=%d hd=%d rotary_half=%d", nq, nkv, hd,
+                  rotary_half);
+  if (act_dtype != cache_dtype)
+    return refuse(ST_BAD_DTYPE, "qk_norm_rope_append: cache dtype %d differs from activations %d",
+                  cache_dtype, act_dtype);
+  const int heads_total = nq + 2 * nkv;
+  const long long warps = (long long)T * heads_total;
+  const int block = 128;
+  const long long grid = (warps * 32 + block - 1) / block;
+  SRLM_DISPATCH_ACT(act_dtype, TA, (qk_norm_rope_append_kernel<TA, TA><<<(unsigned)grid, block, 0, stream>>>(
+      (const TA*)qkv, (TA*)q_out, (TA*)k_cache, (TA*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t,
+      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv)));
+  return launched();
+}

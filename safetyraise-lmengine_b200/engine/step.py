@@ -1,0 +1,232 @@
+"""The step function: one ragged batch through the model, from the cache.
+
+``Engine.step(entries)`` takes, for each request in the batch, the request's
+slot, its next tokens and the places among them whose logits are wanted.
+Portions of prompts stand beside single decoded tokens, cut anywhere.  It
+checks everything on the host first (a refused step launches nothing and
+changes nothing), reserves pages, runs only the given tokens as one batch, and
+commits the new lengths.  It returns float32 logits [wanted, vocab] in the
+order of the entries and of their ``want`` lists.
+
+Counterpart of NativeModel::forward (src/model/native.rs:231-312), which takes
+one request at a time; batching several requests into one forward is this
+engine's own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import architecture_of, read_config_json
+from ..errors import ConfigError, ResourceExhausted, ShapeError, Unavailable
+from ..parts.base import ModelContext, StepContext, Workspace
+from ..weights.safetensors_io import WeightFolder
+
+DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16,
+          "bf16": torch.bfloat16}
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # indices into ``tokens`` whose logits are returned
+
+
+def _round_up(a: int, b: int) -> int:
+    return (a + b - 1) // b * b
+
+
+class Engine:
+    """A model, its cache and its workspace on one GPU."""
+
+    def __init__(self, model, cache: CacheManager, mctx: ModelContext, max_context: int):
+        self.model, self.cache, self.mctx = model, cache, mctx
+        self.spec = model.spec
+        self.max_context = min(max_context, self.spec.max_position_embeddings)
+        self.workspace = Workspace(mctx.device, mctx.max_batch_tokens)
+        self.max_pages_per_request = (self.max_context + cache.page_size - 1) // cache.page_size
+        self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_hosts: list = []          # ring of pinned buffers, each with the event of its last copy
+        self._meta_turn = 0
+        self.steps_run = 0
+
+    # ---- construction -----------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
+        config = read_config_json(model_dir)
+        return cls.from_source(config, WeightFolder(model_dir), dtype=dtype, **kw)
+
+    @classmethod
+    def from_source(cls, config: dict, source, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                    num_pages: Optional[int] = None, max_requests: int = 64,
+                    max_batch_tokens: int = 2048, max_context: Optional[int] = None,
+                    options: Optional[dict] = None) -> "Engine":
+        if not torch.cuda.is_available():
+            raise Unavailable("no CUDA device: this engine has no CPU path")
+        tdtype = DTYPES.get(dtype, dtype)
+        if tdtype not in (torch.float32, torch.bfloat16):
+            raise ConfigError(f"dtype {dtype!r}: float32 or bfloat16")
+        arch = architecture_of(config)
+        spec = arch.read_spec(config)
+        device = torch.device(device)
+        mctx = ModelContext(device, tdtype, max_batch_tokens, dict(options or {}))
+        with torch.cuda.device(device):
+            model = arch.build_model(spec, mctx, source)
+            max_context = min(max_context or spec.max_position_embeddings, spec.max_position_embeddings)
+            groups = model.cache_groups()
+            if num_pages is None:
+                per_page = max(1, sum(g.bytes_per_token(tdtype) for g in groups) * page_size)
+                free, _ = torch.cuda.mem_get_info(device)
+                num_pages = max(1, min(int(free * 0.8) // per_page,
+                                       max_requests * ((max_context + page_size - 1) // page_size)))
+            cache = CacheManager(groups, page_size, num_pages, max_requests, tdtype, device)
+        return cls(model, cache, mctx, max_context)
+
+    # ---- requests ---------------------------------------------------------
+    def open_request(self) -> int:
+        return self.cache.open_request()
+
+    def close_request(self, slot: int) -> None:
+        self.cache.close_request(slot)
+
+    # ---- the step -------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]):
+        if not entries:
+            raise ShapeError("a step needs at least one entry")
+        seen = set()
+        total = 0
+        vocab = self.spec.vocab_size
+        for e in entries:
+            if e.slot in seen:
+                raise ShapeError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            n = len(e.tokens)
+            if n == 0:
+                raise ShapeError("an entry without tokens")
+            start = self.cache.length(e.slot)
+            if start < 0:
+                raise ShapeError(f"slot {e.slot} is not open")
+            if start + n > self.max_context:
+                raise ShapeError(f"slot {e.slot}: {start}+{n} tokens exceed the context of {self.max_context}")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise ShapeError(f"token id {t} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ShapeError(f"wanted place {w} is outside the entry's {n} tokens")
+            total += n
+        if total > self.mctx.max_batch_tokens:
+            raise ShapeError(f"{total} tokens in one step exceed max_batch_tokens={self.mctx.max_batch_tokens}")
+
+    def _meta_buffers(self, words: int):
+        """A pinned host buffer that no copy in flight still reads, and the device buffer."""
+        if self._meta_dev is None or self._meta_dev.numel() < words:
+            cap = max(words, 4 * self.mctx.max_batch_tokens + 64 * (self.max_pages_per_request + 8) + 1024)
+            torch.cuda.synchronize(self.mctx.device)
+            self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.mctx.device)
+            self._meta_hosts = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), None]
+                                for _ in range(4)]
+        self._meta_turn = (self._meta_turn + 1) % len(self._meta_hosts)
+        pair = self._meta_hosts[self._meta_turn]
+        if pair[1] is not None:
+            pair[1].synchronize()
+        return pair, self._meta_dev
+
+    def build_context(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
+        """Flattens the batch, uploads it in one copy and returns the device views."""
+        n = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        groups = self.cache.paged_groups
+        ps = self.cache.page_size
+        kv_lens = [s + q for s, q in zip(starts, q_lens)]
+        pages = _round_up(max(1, max((l + ps - 1) // ps for l in kv_lens)), 8)
+        R = sum(len(e.want) for e in entries)
+        # layout, in int32 words; every section starts on a 16-byte boundary
+        sections, off = {}, 0
+        def place(name, count):
+            nonlocal off
+            sections[name] = (off, count)
+            off = _round_up(off + count, 4)
+        for name in ("token_ids", "positions", "entry_of_token"):
+            place(name, T)
+        for g in groups:
+            place("kv_slot:" + g.name, T)
+        place("slots", n)
+        place("cu_q", n + 1)
+        place("kv_lens", n)
+        place("logit_rows", R)
+        for g in groups:
+            place("table:" + g.name, n * pages)
+        pair, dev = self._meta_buffers(off)
+        host = pair[0]
+        h = host.numpy()
+        view = lambda name: h[sections[name][0]:sections[name][0] + sections[name][1]]
+        tok, posv, eot = view("token_ids"), view("positions"), view("entry_of_token")
+        cu = view("cu_q")
+        rows = view("logit_rows")
+        cu[0] = 0
+        t0 = r0 = 0
+        tables = {g.name: [self.cache.table(g.name, e.slot) for e in entries] for g in groups}
+        for i, e in enumerate(entries):
+            q = q_lens[i]
+            tok[t0:t0 + q] = np.asarray(e.tokens, dtype=np.int32)
+            posv[t0:t0 + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
+            eot[t0:t0 + q] = i
+            for w in e.want:
+                rows[r0] = t0 + int(w)
+                r0 += 1
+            for g in groups:
+                tab = np.asarray(tables[g.name][i], dtype=np.int32)
+                p = posv[t0:t0 + q]
+                view("kv_slot:" + g.name)[t0:t0 + q] = tab[p // ps] * ps + p % ps
+                tv = view("table:" + g.name)[i * pages:(i + 1) * pages]
+                tv[:len(tab)] = tab
+                tv[len(tab):] = 0
+            t0 += q
+            cu[i + 1] = t0
+        view("slots")[:] = [e.slot for e in entries]
+        view("kv_lens")[:] = kv_lens
+        dev[:off].copy_(host[:off], non_blocking=True)
+        pair[1] = torch.cuda.Event()
+        pair[1].record()
+        d = lambda name: dev[sections[name][0]:sections[name][0] + sections[name][1]]
+        return StepContext(
+            T=T, n_entries=n, token_ids=d("token_ids"), positions=d("positions"),
+            entry_of_token=d("entry_of_token"), slots=d("slots"), cu_q=d("cu_q"), kv_lens=d("kv_lens"),
+            logit_rows=d("logit_rows"),
+            block_tables={g.name: d("table:" + g.name).view(n, pages) for g in groups},
+            kv_slot={g.name: d("kv_slot:" + g.name) for g in groups},
+            host={"q_lens": q_lens, "starts": starts, "kv_lens": kv_lens, "slots": [e.slot for e in entries]},
+            cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""
+        self._validate(entries)
+        starts = [self.cache.length(e.slot) for e in entries]
+        done = []
+        for e, s in zip(entries, starts):
+            if not self.cache.reserve(e.slot, s + len(e.tokens)):
+                for e2, s2 in done:                     # give back what this step took
+                    self.cache.truncate(e2.slot, s2)
+                raise ResourceExhausted(f"no free cache pages for slot {e.slot} "
+                                        f"({s}+{len(e.tokens)} tokens); nothing was run")
+            done.append((e, s))
+        try:
+            with torch.cuda.device(self.mctx.device):
+                ctx = self.build_context(entries, starts)
+                logits = self.model.forward(ctx)
+        except Exception:
+            for e, s in done:
+                self.cache.truncate(e.slot, s)
+            raise
+        for e, s in done:
+            self.cache.commit(e.slot, s + len(e.tokens))
+        self.steps_run += 1
+        return logits

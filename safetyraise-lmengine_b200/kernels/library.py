@@ -1,0 +1,146 @@
+"""Loads ``libsrlm_kernels.so`` and wraps each exported kernel for torch tensors.
+
+There is no other implementation behind these functions: if the library cannot
+be built or loaded, or a tensor is not on a CUDA device, the call raises.
+Tensors are passed as raw device pointers; every launch goes to torch's
+current stream, so the calls can be recorded into a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..errors import ShapeError, Unavailable
+
+DT_F32, DT_BF16 = 0, 1
+_CODES = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _CODES[dt]
+    except KeyError:
+        raise ShapeError(f"dtype {dt} is not taken by the kernels (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return C.c_void_p(0)
+    if not t.is_cuda:
+        raise Unavailable("kernels take CUDA tensors only; there is no CPU path")
+    if not t.is_contiguous():
+        raise ShapeError("kernels take contiguous tensors")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class KernelLibrary:
+    def __init__(self):
+        self._lib = None
+
+    @property
+    def lib(self):
+        if self._lib is None:
+            from ..csrc.build import build_kernels
+            try:
+                path = build_kernels()
+                self._lib = C.CDLL(path)
+            except Exception as e:   # noqa: BLE001
+                raise Unavailable(f"the CUDA kernel library is missing and could not be built: {e}") from e
+            self._lib.srlm_last_error.restype = C.c_char_p
+        return self._lib
+
+    def _check(self, status: int, what: str):
+        if status != 0:
+            msg = self.lib.srlm_last_error().decode(errors="replace")
+            if status < 0:
+                raise ShapeError(f"{what} refused: {msg}")
+            raise RuntimeError(f"{what} failed with CUDA error {status}: {msg}")
+
+    # ---- elementwise -----------------------------------------------------
+    def embed_gather(self, ids, table, out, bad_flag):
+        T, H = out.shape
+        self._check(self.lib.srlm_embed_gather(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out),
+                                               C.c_int(T), C.c_int(H), C.c_int(table.shape[0]),
+                                               _ptr(bad_flag), _stream()), "embed_gather")
+
+    def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None, unit_offset=False):
+        R, H = out.shape
+        self._check(self.lib.srlm_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), C.c_float(eps),
+                                              _ptr(out), dtype_code(out.dtype), _ptr(rows), C.c_int(R),
+                                              C.c_int(H), C.c_int(int(unit_offset)), _stream()),
+                    "add_rmsnorm")
+
+    def swiglu(self, gate_up, out):
+        T, I = out.shape
+        self._check(self.lib.srlm_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), C.c_int(T),
+                                         C.c_int(I), _stream()), "swiglu")
+
+    def cast(self, src, dst):
+        self._check(self.lib.srlm_cast(_ptr(src), dtype_code(src.dtype), _ptr(dst), dtype_code(dst.dtype),
+                                       C.c_longlong(src.numel()), _stream()), "cast")
+
+    def residual_add(self, residual, delta):
+        self._check(self.lib.srlm_residual_add(_ptr(residual), _ptr(delta), dtype_code(delta.dtype),
+                                               C.c_longlong(delta.numel()), _stream()), "residual_add")
+
+    # ---- position encoding and cache append ------------------------------
+    def rope_table(self, positions, cos, sin, theta, rotary_dim):
+        T, half = cos.shape
+        self._check(self.lib.srlm_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), C.c_int(T), C.c_int(half),
+                                             C.c_double(theta), C.c_int(rotary_dim), _stream()), "rope_table")
+
+    def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos, sin, kv_slot,
+                            nq, nkv, hd, rotary_half, write_kv=True):
+        T = qkv.shape[0]
+        self._check(self.lib.srlm_qk_norm_rope_append(
+            _ptr(qkv), _ptr(q_out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
+            dtype_code(k_cache.dtype), _ptr(q_norm_w), _ptr(k_norm_w), C.c_float(eps), _ptr(cos), _ptr(sin),
+            _ptr(kv_slot), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(rotary_half),
+            C.c_int(int(write_kv)), _stream()), "qk_norm_rope_append")
+
+    # ---- attention --------------------------------------------------------
+    def paged_attention_simt(self, q, k_cache, v_cache, out, block_table, entry_of_token, positions,
+                             nq, nkv, hd, page_size, scale, window=0):
+        T = q.shape[0]
+        self._check(self.lib.srlm_paged_attention_simt(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(q.dtype), dtype_code(k_cache.dtype),
+            _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(entry_of_token), _ptr(positions),
+            C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale),
+            C.c_int(window or 0), _stream()), "paged_attention_simt")
+
+    # ---- matrix products ----------------------------------------------------
+    def gemm_tn_simt(self, a, w, out):
+        """out[M,N] = a[M,K] @ w[N,K]^T, float32 FMA accumulation."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise ShapeError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.srlm_gemm_tn_simt(
+            _ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype),
+            C.c_int(M), C.c_int(N), C.c_int(K), C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)),
+            C.c_longlong(out.stride(0)), _stream()), "gemm_tn_simt")
+
+    def gemm(self, a, w, out):
+        """The product path's matrix product: picks the kernel for the dtypes and sizes."""
+        self.gemm_tn_simt(a, w, out)
+
+    def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
+                        window=0):
+        """The product path's attention over the cache for the batch of ``ctx``."""
+        self.paged_attention_simt(q, k_cache, v_cache, out, block_table, ctx.entry_of_token, ctx.positions,
+                                  nq, nkv, hd, page_size, scale, window)
+
+    # ---- sampling -------------------------------------------------------------
+    def argmax(self, logits, out_tokens, bad_flag):
+        n, V = logits.shape
+        self._check(self.lib.srlm_argmax(_ptr(logits), C.c_longlong(logits.stride(0)), C.c_int(n), C.c_int(V),
+                                         _ptr(out_tokens), _ptr(bad_flag), _stream()), "argmax")
+
+
+ops = KernelLibrary()

@@ -1,0 +1,78 @@
+"""Attention over the paged cache with grouped query heads.
+
+Per step: fused q/k/v projection, per-head RMSNorm of q and k (if the
+specification has one), position encoding, append of k and v to the pages,
+causal attention over everything the request has in the cache, output
+projection.  src/model/native.rs:565-648.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..cache.manager import PAGED_ALL, PAGED_WINDOW
+from ..config.spec import AttentionSpec, RunStep
+from ..errors import Unsupported
+from ..kernels import ops
+from ..weights.loader import MATRIX, VECTOR, TensorDecl
+from .base import POSITION_ENCODINGS, CacheNeed, Part, lookup, register_mixer
+from .linear import Linear
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Part):
+    def __init__(self, spec: AttentionSpec, prefix: str, tensors: dict, mctx):
+        if spec.bias:
+            raise Unsupported("attention with bias is not implemented")
+        self.spec = spec
+        p = prefix + "self_attn."
+        # q, k and v rows stacked: one projection, one read of the input
+        self.qkv = Linear(torch.cat([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
+                                     tensors[p + "v_proj.weight"]], dim=0).contiguous(), p + "qkv")
+        self.out = Linear(tensors[p + "o_proj.weight"], p + "o_proj")
+        self.q_norm_w = tensors[p + "q_norm.weight"] if spec.qk_norm else None
+        self.k_norm_w = tensors[p + "k_norm.weight"] if spec.qk_norm else None
+        self.eps = spec.qk_norm.eps if spec.qk_norm else 1.0
+        self.position = None
+        if spec.position is not None:
+            self.position = lookup(POSITION_ENCODINGS, spec.position.kind, "position encoding")(
+                spec.position, mctx)
+        self.options = mctx.options
+
+    @classmethod
+    def tensor_decls(cls, spec: AttentionSpec, prefix: str) -> List[TensorDecl]:
+        p = prefix + "self_attn."
+        qd, kvd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        decls = [TensorDecl(p + "q_proj.weight", (qd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + "k_proj.weight", (kvd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + "v_proj.weight", (kvd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + "o_proj.weight", (spec.hidden_size, qd), MATRIX)]
+        if spec.qk_norm:
+            decls += [TensorDecl(p + "q_norm.weight", (spec.head_dim,), VECTOR),
+                      TensorDecl(p + "k_norm.weight", (spec.head_dim,), VECTOR)]
+        return decls
+
+    def cache_need(self) -> CacheNeed:
+        s = self.spec
+        return CacheNeed(PAGED_WINDOW if s.window else PAGED_ALL, s.kv_heads, s.head_dim, s.window)
+
+    def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
+        s = self.spec
+        T = x.shape[0]
+        qkv = self.qkv(ctx, x, "attn.qkv")
+        k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
+        q = ctx.workspace.get("attn.q", T, s.heads * s.head_dim, ctx.dtype)
+        if self.position is not None:
+            cos, sin = self.position.tables(ctx)
+            half = self.position.half
+        else:
+            cos = sin = None
+            half = 0
+        ops.qk_norm_rope_append(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, self.eps, cos, sin,
+                                ctx.kv_slot[group], s.heads, s.kv_heads, s.head_dim, half,
+                                write_kv=run_step.writes_cache)
+        attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
+        ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
+                            s.head_dim, k_pool.shape[1], s.softmax_scale, s.window or 0)
+        return self.out(ctx, attended, "attn.proj")

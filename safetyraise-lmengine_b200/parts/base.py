@@ -1,0 +1,128 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A part is built from its own specification (sizes and constants as fields) and
+the tensors it declared; it never learns which model it is in.  Five kinds:
+
+* Norm:             ``apply(residual, delta, out, rows=None)``
+* PositionEncoding: ``prepare(ctx)`` once per step; a mixer asks it for its tables
+* Mixer:            ``cache_need()``, ``forward(ctx, x, run_step) -> [T, hidden]``
+* FeedForward:      ``forward(ctx, x) -> [T, hidden]``
+* Block:            ``forward(ctx, residual, pending, run_step) -> pending``
+
+Each kind has a registry from the ``kind`` string of its specification to the
+class; ``register_*`` adds to it, from inside or outside this package.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..errors import Unsupported
+from ..weights.loader import TensorDecl
+
+NORMS: Dict[str, type] = {}
+POSITION_ENCODINGS: Dict[str, type] = {}
+MIXERS: Dict[str, type] = {}
+FEED_FORWARDS: Dict[str, type] = {}
+BLOCKS: Dict[str, type] = {}
+
+
+def _register(table, what):
+    def deco(kind: str):
+        def wrap(cls):
+            table[kind] = cls
+            cls.kind = kind
+            return cls
+        return wrap
+    deco.__doc__ = f"Class decorator: registers a {what} under a kind string."
+    return deco
+
+
+register_norm = _register(NORMS, "norm")
+register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_mixer = _register(MIXERS, "mixer")
+register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
+register_block = _register(BLOCKS, "block")
+
+
+def lookup(table, kind: str, what: str):
+    if kind not in table:
+        raise Unsupported(f"{what} kind {kind!r} is not registered (registered: {sorted(table)})")
+    return table[kind]
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What one run step of a mixer needs from the cache manager."""
+    kind: str                                 # cache.manager.PAGED_ALL | PAGED_WINDOW | FIXED_STATE | "none"
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None
+    state_shape: Tuple[int, ...] = ()
+    state_dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class ModelContext:
+    """What every part of one model instance shares."""
+    device: torch.device
+    dtype: torch.dtype                        # activation / cache dtype: float32 or bfloat16
+    max_batch_tokens: int
+    options: dict = field(default_factory=dict)
+
+
+class Workspace:
+    """Named activation buffers, allocated once at their largest size and reused every step."""
+
+    def __init__(self, device, max_tokens: int):
+        self.device, self.max_tokens = device, max_tokens
+        self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+
+    def get(self, name: str, rows: int, width: int, dtype: torch.dtype, reserve=None) -> torch.Tensor:
+        """A [rows, width] view of the buffer ``name``; the buffer is made for ``reserve`` rows
+        (default: the most tokens a step may hold) and grows if a step ever needs more."""
+        key = (name, width, dtype)
+        buf = self._bufs.get(key)
+        cap = max(rows, self.max_tokens if reserve is None else reserve, 1)
+        if buf is None or buf.shape[0] < rows:
+            buf = torch.empty((cap, width), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:rows]
+
+
+@dataclass
+class StepContext:
+    """The ragged batch of one step, flattened, on the device.
+
+    Entry e feeds q_lens[e] tokens of the request in slot slots[e], at positions
+    starts[e] .. starts[e]+q_lens[e]-1.  Paged groups add a block table per entry
+    and, for every token, the flat cache row it is written to.
+    """
+    T: int
+    n_entries: int
+    token_ids: torch.Tensor                   # int32 [T]
+    positions: torch.Tensor                   # int32 [T]
+    entry_of_token: torch.Tensor              # int32 [T]
+    slots: torch.Tensor                       # int32 [n_entries]
+    cu_q: torch.Tensor                        # int32 [n_entries + 1]
+    kv_lens: torch.Tensor                     # int32 [n_entries] (after this step)
+    logit_rows: torch.Tensor                  # int32 [R]
+    block_tables: Dict[str, torch.Tensor]     # group -> int32 [n_entries, pages]
+    kv_slot: Dict[str, torch.Tensor]          # group -> int32 [T]
+    host: dict                                # the same as Python lists, for parts that plan on the host
+    cache: "object"
+    workspace: Workspace
+    dtype: torch.dtype
+    tables: dict = field(default_factory=dict)    # position-encoding tables of this step
+    max_q_len: int = 1
+    max_kv_len: int = 1
+
+
+class Part:
+    """Common behaviour: a part declares its tensors before it is built."""
+
+    @classmethod
+    def tensor_decls(cls, spec, prefix: str) -> List[TensorDecl]:
+        return []

@@ -1,0 +1,55 @@
+import json
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+# Two tiny Qwen3 configurations that differ in every size and option.
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 128,
+    "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 256, "vocab_size": 384, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 256,
+    "eos_token_id": [7, 9],
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+
+
+def make_folder(tmp_path_factory_or_dir, config, seed, name="model"):
+    from safetyraise_lmengine_b200.weights.random_init import write_model_folder
+    base = tmp_path_factory_or_dir
+    out = str(base.mktemp(name)) if hasattr(base, "mktemp") else os.path.join(str(base), name)
+    return write_model_folder(config, seed, out)
+
+
+@pytest.fixture(scope="session")
+def folder_a(tmp_path_factory):
+    return make_folder(tmp_path_factory, TINY_A, 0, "tiny_a")
+
+
+@pytest.fixture(scope="session")
+def folder_b(tmp_path_factory):
+    return make_folder(tmp_path_factory, TINY_B, 1, "tiny_b")
+
+
+@pytest.fixture(scope="session", params=["A", "B"])
+def tiny_folder(request, tmp_path_factory):
+    cfg, seed = TINY[request.param]
+    return request.param, make_folder(tmp_path_factory, cfg, seed, "tiny_" + request.param.lower())

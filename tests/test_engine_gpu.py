@@ -1,0 +1,153 @@
+"""The engine against the plain implementation, under every way of cutting the work."""
+import numpy as np
+import pytest
+import torch
+from conftest import TINY
+from helpers import (TOL, check_against_plain, cut_bulk_tail, cut_portions, cut_whole, plain_logits,
+                     random_tokens, rel_err, replay)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def build(folder, dtype, num_pages=64, page_size=16, **kw):
+    from safetyraise_lmengine_b200 import Engine
+    return Engine.from_folder(folder, dtype=dtype, page_size=page_size, num_pages=num_pages,
+                              max_requests=4, max_batch_tokens=512, **kw)
+
+
+def requests_for(name, seed=0):
+    cfg, _ = TINY[name]
+    rng = np.random.default_rng(100 + seed)
+    lens = [5, 11, 17, 70] if name == "A" else [1, 7, 33, 64, 100]
+    return {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_whole_requests_alone(tiny_folder, dtype):
+    name, folder = tiny_folder
+    eng = build(folder, dtype)
+    reqs = requests_for(name)
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_whole(rid, toks)))
+    check_against_plain(got, folder, reqs, dtype)
+    assert eng.cache.audit() == 0 and eng.cache.free_pages() == 64
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bulk_then_last_32_one_by_one(tiny_folder, dtype):
+    name, folder = tiny_folder
+    eng = build(folder, dtype)
+    reqs = {k: v for k, v in requests_for(name).items() if len(v) >= 33}
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_bulk_tail(rid, toks, 32)))
+    check_against_plain(got, folder, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("page_size", [4, 16])
+def test_portions_of_changing_size(tiny_folder, dtype, page_size):
+    name, folder = tiny_folder
+    eng = build(folder, dtype, num_pages=40, page_size=page_size)
+    reqs = requests_for(name)
+    got = {}
+    for rid, toks in reqs.items():
+        if len(toks) < 2:
+            continue
+        got.update(replay(eng, cut_portions(rid, toks)))
+    check_against_plain(got, folder, {k: v for k, v in reqs.items() if len(v) >= 2}, dtype)
+
+
+def mixed_schedule(reqs, chunk=8):
+    """Up to four live requests; portions of prompts beside single tokens of requests whose last 6
+    tokens are fed one at a time; a finished request's pages go to the next one."""
+    order = list(reqs)
+    live, waiting, steps = [], list(order), []
+    fed = {r: 0 for r in order}
+    while live or waiting:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        entries, ended = [], []
+        for r in live:
+            toks = reqs[r]
+            left = len(toks) - fed[r]
+            n = 1 if left <= 6 else min(chunk + (len(steps) % 3), left - 6)
+            entries.append((r, toks[fed[r]:fed[r] + n], list(range(n))))
+            fed[r] += n
+            if fed[r] == len(toks):
+                ended.append(r)
+        steps.append({"entries": entries, "end": ended})
+        live = [r for r in live if r not in ended]
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixed_batches_with_page_reuse(tiny_folder, dtype):
+    name, folder = tiny_folder
+    cfg, _ = TINY[name]
+    rng = np.random.default_rng(7)
+    lens = [23, 9, 41, 30, 17, 55, 12, 38]
+    reqs = {f"m{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
+    page = 4
+    # room for the four largest at once, far less than all eight: pages must be used again
+    num_pages = sum(sorted((n + page - 1) // page for n in lens)[-4:])
+    eng = build(folder, dtype, num_pages=num_pages, page_size=page)
+    # poison the pools so that a stale or unwritten page shows
+    for pool in eng.cache.kv_pools.values():
+        pool.fill_(float("nan"))
+    got = replay(eng, mixed_schedule(reqs))
+    check_against_plain(got, folder, reqs, dtype)
+    taken, reused = eng.cache.reuse_counts()
+    assert reused > 0 and taken > num_pages
+    assert eng.cache.audit() == 0 and eng.cache.free_pages() == num_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cuttings_agree_with_each_other(folder_b, dtype):
+    """Beyond agreeing with the oracle: the float32 path gives the same bits however the work is cut."""
+    eng = build(folder_b, dtype)
+    toks = requests_for("B")["r4"]
+    a = replay(eng, cut_whole("x", toks))
+    b = replay(eng, cut_bulk_tail("x", toks, 32))
+    c = replay(eng, cut_portions("x", toks))
+    for p in range(len(toks)):
+        if dtype == "float32":
+            assert np.array_equal(a[("x", p)], b[("x", p)]) and np.array_equal(a[("x", p)], c[("x", p)]), p
+        else:
+            scale = np.abs(a[("x", p)]).max()
+            assert np.abs(a[("x", p)] - b[("x", p)]).max() <= TOL[dtype] * scale
+            assert np.abs(a[("x", p)] - c[("x", p)]).max() <= TOL[dtype] * scale
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_and_long_decoding(folder_b, dtype):
+    cfg, _ = TINY["B"]
+    rng = np.random.default_rng(3)
+    toks = random_tokens(rng, 200, cfg["vocab_size"])
+    eng = build(folder_b, dtype)
+    steps = [{"entries": [("d", toks[i:i + 1], [0])]} for i in range(len(toks))]
+    got = replay(eng, steps)
+    check_against_plain(got, folder_b, {"d": toks}, dtype)
+
+
+def test_refused_step_changes_nothing(folder_a):
+    from safetyraise_lmengine_b200 import StepEntry
+    from safetyraise_lmengine_b200.errors import ResourceExhausted, ShapeError
+    eng = build(folder_a, "float32", num_pages=3, page_size=4)
+    s = eng.open_request()
+    ref = eng.step([StepEntry(s, [1, 2, 3, 4, 5], [4])]).cpu().numpy().copy()
+    free = eng.cache.free_pages()
+    with pytest.raises(ShapeError):
+        eng.step([StepEntry(s, [1, 999], [0])])                  # id outside the vocabulary
+    with pytest.raises(ResourceExhausted):
+        eng.step([StepEntry(s, list(range(20)), [0])])            # more pages than exist
+    with pytest.raises(ShapeError):
+        eng.step([StepEntry(s, [], [])])
+    assert eng.cache.length(s) == 5 and eng.cache.free_pages() == free and eng.cache.audit() == 0
+    eng.close_request(s)
+    s2 = eng.open_request()
+    again = eng.step([StepEntry(s2, [1, 2, 3, 4, 5], [4])]).cpu().numpy()
+    assert np.array_equal(ref, again)

@@ -1,0 +1,266 @@
+"""Each kernel alone against a plain float32 formula in torch, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+ACT = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from safetyraise_lmengine_b200.kernels import ops as o
+    return o
+
+
+def tol(dt):
+    return dict(rtol=1e-5, atol=1e-5) if dt == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("H", [1, 5, 255, 256, 257, 4096])
+@pytest.mark.parametrize("wdt", ACT)
+def test_embed_gather(H, wdt):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    table = torch.randn(37, H, device=DEV, generator=g).to(wdt)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, H, device=DEV)
+    bad = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embed_gather(ids, table, out, bad)
+    assert torch.equal(out, table.float()[ids.long()]) and bad.item() == 0
+    ids[2] = 37
+    ops().embed_gather(ids, table, out, bad)
+    assert bad.item() == 1 and torch.all(out[2] == 0)
+
+
+@pytest.mark.parametrize("H", [4, 5, 255, 256, 257, 1000, 4096, 5120])
+@pytest.mark.parametrize("dt", ACT)
+@pytest.mark.parametrize("eps", [1e-6, 1e-2])
+def test_add_rmsnorm(H, dt, eps):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    T = 7
+    res = torch.randn(T, H, device=DEV, generator=g) * 3
+    delta = torch.randn(T, H, device=DEV, generator=g).to(dt)
+    w = 1 + 0.1 * torch.randn(H, device=DEV, generator=g)
+    x = res + delta.float()
+    ref = x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+    out = torch.empty(T, H, device=DEV, dtype=dt)
+    r = res.clone()
+    ops().add_rmsnorm(r, delta, w, eps, out)
+    assert torch.allclose(r, x, rtol=0, atol=0)
+    assert torch.allclose(out.float(), ref, **tol(dt))
+    # gathered rows, residual untouched, no delta
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, H, device=DEV, dtype=dt)
+    r2 = res.clone()
+    ops().add_rmsnorm(r2, None, w, eps, out2, rows=rows)
+    ref2 = res * torch.rsqrt((res.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+    assert torch.equal(r2, res)
+    assert torch.allclose(out2.float(), ref2[rows.long()], **tol(dt))
+    # gathered rows with delta: residual untouched
+    ops().add_rmsnorm(r2, delta, w, eps, out2, rows=rows)
+    assert torch.equal(r2, res) and torch.allclose(out2.float(), ref[rows.long()], **tol(dt))
+
+
+@pytest.mark.parametrize("I", [1, 5, 257, 12288])
+@pytest.mark.parametrize("dt", ACT)
+def test_swiglu(I, dt):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    gu = (torch.randn(9, 2 * I, device=DEV, generator=g) * 4).to(dt)
+    out = torch.empty(9, I, device=DEV, dtype=dt)
+    ops().swiglu(gu, out)
+    gate, up = gu.float()[:, :I], gu.float()[:, I:]
+    ref = gate * torch.sigmoid(gate) * up
+    assert torch.allclose(out.float(), ref, **tol(dt))
+
+
+@pytest.mark.parametrize("theta, rd", [(1e4, 16), (1e6, 128), (5e5, 48)])
+def test_rope_table(theta, rd):
+    pos = torch.tensor([0, 1, 2, 77, 4095, 131071], dtype=torch.int32, device=DEV)
+    half = rd // 2
+    cos = torch.empty(len(pos), half, device=DEV)
+    sin = torch.empty_like(cos)
+    ops().rope_table(pos, cos, sin, theta, rd)
+    i = torch.arange(half, dtype=torch.float64)
+    ang = pos.cpu().double()[:, None] / (theta ** (2 * i / rd))[None, :]
+    assert torch.allclose(cos.cpu().double(), torch.cos(ang), rtol=0, atol=1e-7)
+    assert torch.allclose(sin.cpu().double(), torch.sin(ang), rtol=0, atol=1e-7)
+
+
+def ref_norm_rope(x, w, eps, cos, sin, half):
+    # x [T, heads, hd] float32
+    if w is not None:
+        x = x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+    l, r = x[..., :half], x[..., half:2 * half]
+    c, s = cos[:, None, :], sin[:, None, :]
+    out = x.clone()
+    out[..., :half] = l * c - r * s
+    out[..., half:2 * half] = r * c + l * s
+    return out
+
+
+@pytest.mark.parametrize("nq, nkv, hd, rd", [(4, 2, 16, 16), (5, 1, 48, 48), (8, 8, 128, 128), (3, 3, 80, 40),
+                                             (6, 2, 256, 256)])
+@pytest.mark.parametrize("dt", ACT)
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_qk_norm_rope_append(nq, nkv, hd, rd, dt, with_norm):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    T, pages, ps = 11, 9, 4
+    eps = 1e-5
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV, generator=g).to(dt)
+    qw = (1 + 0.1 * torch.randn(hd, device=DEV, generator=g)) if with_norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device=DEV, generator=g)) if with_norm else None
+    pos = torch.tensor([3, 4, 5, 0, 1, 2, 3, 100, 101, 7, 8], dtype=torch.int32, device=DEV)
+    half = rd // 2
+    cos = torch.empty(T, half, device=DEV)
+    sin = torch.empty_like(cos)
+    ops().rope_table(pos, cos, sin, 1e4, rd)
+    slots = torch.randperm(pages * ps, device=DEV, generator=g)[:T].to(torch.int32)
+    slots[5] = -1                                   # this token's keys are not kept
+    kc = torch.full((pages, ps, nkv, hd), 7.0, device=DEV, dtype=dt)
+    vc = torch.full((pages, ps, nkv, hd), 7.0, device=DEV, dtype=dt)
+    q = torch.empty(T, nq * hd, device=DEV, dtype=dt)
+    ops().qk_norm_rope_append(qkv, q, kc, vc, qw, kw, eps, cos, sin, slots, nq, nkv, hd, half)
+    x = qkv.float().view(T, nq + 2 * nkv, hd)
+    q_ref = ref_norm_rope(x[:, :nq], qw, eps, cos, sin, half)
+    k_ref = ref_norm_rope(x[:, nq:nq + nkv], kw, eps, cos, sin, half)
+    v_ref = x[:, nq + nkv:]
+    assert torch.allclose(q.float().view(T, nq, hd), q_ref, **tol(dt))
+    kflat, vflat = kc.float().view(pages * ps, nkv, hd), vc.float().view(pages * ps, nkv, hd)
+    for t in range(T):
+        if slots[t] < 0:
+            continue
+        assert torch.allclose(kflat[slots[t]], k_ref[t], **tol(dt))
+        assert torch.equal(vflat[slots[t]], v_ref[t].to(dt).float())
+    untouched = torch.ones(pages * ps, dtype=torch.bool, device=DEV)
+    untouched[slots[slots >= 0].long()] = False
+    assert torch.all(kflat[untouched] == 7.0) and torch.all(vflat[untouched] == 7.0)
+    # a step that only reads another step's cache leaves it alone
+    kc2, vc2 = kc.clone(), vc.clone()
+    ops().qk_norm_rope_append(qkv, q, kc2, vc2, qw, kw, eps, cos, sin, slots, nq, nkv, hd, half, write_kv=False)
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)
+
+
+def ref_paged_attention(q, kc, vc, tables, entry_of_token, positions, nq, nkv, hd, ps, scale, window):
+    T = q.shape[0]
+    out = torch.zeros(T, nq, hd, dtype=torch.float64)
+    qd, kd, vd = q.double().cpu().view(T, nq, hd), kc.double().cpu(), vc.double().cpu()
+    for t in range(T):
+        e, p = int(entry_of_token[t]), int(positions[t])
+        lo = max(0, p - window + 1) if window else 0
+        js = torch.arange(lo, p + 1)
+        rows = torch.tensor([tables[e][j // ps] for j in js.tolist()]) * ps + js % ps
+        kf, vf = kd.view(-1, nkv, hd)[rows], vd.view(-1, nkv, hd)[rows]
+        for h in range(nq):
+            kh = h // (nq // nkv)
+            s = (kf[:, kh] @ qd[t, h]) * scale
+            pr = torch.softmax(s, 0)
+            out[t, h] = pr @ vf[:, kh]
+    return out
+
+
+def make_paged_case(nq, nkv, hd, ps, dt, lens_q, lens_kv, seed=5, pages=64):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    n = len(lens_q)
+    T = sum(lens_q)
+    kc = torch.randn(pages, ps, nkv, hd, device=DEV, generator=g).to(dt)
+    vc = torch.randn(pages, ps, nkv, hd, device=DEV, generator=g).to(dt)
+    q = torch.randn(T, nq * hd, device=DEV, generator=g).to(dt)
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    tables, used = [], 0
+    for kv in lens_kv:
+        need = (kv + ps - 1) // ps
+        tables.append(perm[used:used + need])
+        used += need
+    assert used <= pages
+    width = max(len(t) for t in tables)
+    bt = torch.zeros(n, width, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    eot, pos = [], []
+    for i, (ql, kv) in enumerate(zip(lens_q, lens_kv)):
+        eot += [i] * ql
+        pos += list(range(kv - ql, kv))
+    return q, kc, vc, tables, bt.to(DEV), torch.tensor(eot, dtype=torch.int32, device=DEV), \
+        torch.tensor(pos, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("nq, nkv, hd, ps", [(4, 2, 16, 4), (6, 1, 32, 16), (8, 2, 128, 16), (5, 5, 80, 8),
+                                             (2, 1, 256, 32)])
+@pytest.mark.parametrize("dt", ACT)
+@pytest.mark.parametrize("window", [0, 9])
+def test_paged_attention_simt(nq, nkv, hd, ps, dt, window):
+    lens_q, lens_kv = [1, 7, 33, 1, 2], [1, 40, 33, 65, 100]
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, dt, lens_q, lens_kv)
+    out = torch.empty_like(q)
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_simt(q, kc, vc, out, bt, eot, pos, nq, nkv, hd, ps, scale, window)
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    t = dict(rtol=1e-4, atol=1e-5) if dt == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, **t)
+
+
+def test_paged_attention_finds_one_far_key():
+    """One key among hundreds carries the mass: a kernel that skips or misplaces it shows at once."""
+    nq, nkv, hd, ps = 4, 2, 32, 16
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.float32, [1], [700], pages=48)
+    out = torch.empty_like(q)
+    for far in (0, 15, 16, 333, 699):
+        kc2 = kc * 0.01
+        page, off = tables[0][far // ps], far % ps
+        kc2[page, off] = q.view(nq, hd)[0::2] * 4.0        # heads 0 and 2 -> kv heads 0 and 1
+        ops().paged_attention_simt(q, kc2, vc, out, bt, eot, pos, nq, nkv, hd, ps, 1.0, 0)
+        got = out.view(nq, hd)
+        for h, kh in ((0, 0), (2, 1)):
+            assert torch.allclose(got[h], vc[page, off, kh], atol=1e-3), (far, h)
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 129, 33), (17, 384, 96),
+                                     (200, 255, 257), (8, 4096, 1024)])
+@pytest.mark.parametrize("dts", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                 (torch.bfloat16, torch.float32)])
+def test_gemm_tn_simt(M, N, K, dts):
+    adt, odt = dts
+    g = torch.Generator(device=DEV).manual_seed(6)
+    a = torch.randn(M, K, device=DEV, generator=g).to(adt)
+    w = torch.randn(N, K, device=DEV, generator=g).to(adt)
+    out = torch.empty(M, N, device=DEV, dtype=odt)
+    ops().gemm_tn_simt(a, w, out)
+    ref = (a.double() @ w.double().T)
+    if odt == torch.float32:
+        assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4 * math.sqrt(K))
+    else:
+        assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    g = torch.Generator(device=DEV).manual_seed(8)
+    a = torch.randn(130, 300, device=DEV, generator=g)
+    w = torch.randn(77, 300, device=DEV, generator=g)
+    full = torch.empty(130, 77, device=DEV)
+    ops().gemm_tn_simt(a, w, full)
+    one = torch.empty(1, 77, device=DEV)
+    ops().gemm_tn_simt(a[97:98].contiguous(), w, one)
+    assert torch.equal(one[0], full[97])
+
+
+def test_argmax_ties_go_to_the_lowest_id():
+    logits = torch.zeros(4, 1000, device=DEV)
+    logits[0, [5, 700]] = 3.0
+    logits[1, 999] = 1.0
+    logits[2] = -1.0
+    logits[3, 512] = 2.0
+    logits[3, 513] = 2.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    bad = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().argmax(logits, out, bad)
+    assert out.tolist() == [5, 999, 0, 512] and bad.item() == 0
+    big = torch.randn(3, 151936, device=DEV)
+    out3 = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops().argmax(big, out3, bad)
+    assert out3.tolist() == big.argmax(-1).tolist()
+    big[1, 7] = float("nan")
+    ops().argmax(big, out3, bad)
+    assert bad.item() == 1
