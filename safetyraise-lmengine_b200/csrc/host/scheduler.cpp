@@ -104,7 +104,10 @@ int Scheduler::plan(std::vector<PlanEntry>* out, std::vector<int64_t>* preempted
     Request& r = requests_[queue_.front()];
     int slot = cache_->open_request();
     if (slot < 0) break;
-    if (cache_->fit_tokens(slot, 1) <= 0) {   // not one page is free
+    // room for the whole first portion, or the request waits: a request that comes in on
+    // the last free page would only be thrown out again
+    const int first = std::min(cfg_.prefill_chunk, r.total_len);
+    if (cache_->fit_tokens(slot, first) < first) {
       cache_->close_request(slot);
       break;
     }

@@ -1,0 +1,222 @@
+"""The Python entry point: load a model, submit requests of token ids, get token ids.
+
+``LLM`` ties the step function, the scheduler and the sampler together the way
+the reference's Engine ties its worker loop (src/engine/scheduler.rs:319-488,
+830-940).  ``EngineConfig`` keeps the reference's option names where it has
+them (src/engine/scheduler.rs:27-61) and adds the ones a paged, batched engine
+needs.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..errors import ConfigError, EngineError, ResourceExhausted
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, fresh_seed
+from .scheduler import (FINISH_CANCELLED, FINISH_DEADLINE, FINISH_ERROR, FINISH_LENGTH, FINISH_STOP,
+                        GenerationRequest, RequestState, Scheduler, Usage)
+from .step import Engine, StepEntry
+
+
+@dataclass
+class EngineConfig:
+    # names of the reference's EngineConfig
+    max_context: int = 4096
+    max_active: int = 8
+    queue_capacity: int = 8
+    prefill_chunk: int = 512
+    max_request_ms: int = 300_000
+    # this engine's own
+    max_batch_tokens: int = 2048
+    page_size: int = 16
+    num_pages: Optional[int] = None        # None: sized from free device memory
+    dtype: str = "bfloat16"
+    device: str = "cuda:0"
+
+    def validate(self) -> None:            # src/engine/scheduler.rs:124-141
+        for name in ("max_context", "max_active", "queue_capacity", "prefill_chunk", "max_request_ms",
+                     "max_batch_tokens", "page_size"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"{name} must be positive")
+        if self.max_active > 1024 or self.queue_capacity > 65536:
+            raise ConfigError("max_active <= 1024 and queue_capacity <= 65536")
+        if self.num_pages is not None and self.num_pages <= 0:
+            raise ConfigError("num_pages must be positive")
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "EngineConfig":
+        unknown = set(d) - set(cls.__dataclass_fields__)
+        if unknown:                        # unknown fields are refused, as serde(deny_unknown_fields) does
+            raise ConfigError(f"unknown engine option(s): {sorted(unknown)}")
+        return cls(**d)
+
+
+@dataclass
+class GenerationResult:
+    request_id: int
+    tokens: List[int]
+    finish_reason: str
+    usage: Usage
+    error: Optional[str] = None
+
+
+class LLM:
+    def __init__(self, engine: Engine, config: EngineConfig):
+        config.validate()
+        self.engine, self.config = engine, config
+        self.scheduler = Scheduler(engine.cache, config.max_active, config.queue_capacity,
+                                   config.prefill_chunk, config.max_batch_tokens,
+                                   min(config.max_context, engine.max_context))
+        self.sampler = Sampler(engine.mctx.device, engine.spec.vocab_size, config.max_active)
+        self.eos = set(engine.spec.eos_token_ids)
+        self._live: Dict[int, RequestState] = {}
+        self._done: Dict[int, RequestState] = {}
+        self._ids = itertools.count(1)
+        self.failed = self.cancelled = 0
+
+    # ---- construction ---------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_path: str, config: Optional[EngineConfig] = None, **overrides) -> "LLM":
+        config = config or EngineConfig()
+        for k, v in overrides.items():
+            if k not in EngineConfig.__dataclass_fields__:
+                raise ConfigError(f"unknown engine option {k!r}")
+            setattr(config, k, v)
+        config.validate()
+        engine = Engine.from_folder(model_path, dtype=config.dtype, device=config.device,
+                                    page_size=config.page_size, num_pages=config.num_pages,
+                                    max_requests=config.max_active, max_batch_tokens=config.max_batch_tokens,
+                                    max_context=config.max_context)
+        return cls(engine, config)
+
+    # ---- requests -----------------------------------------------------------------
+    def submit(self, request: GenerationRequest) -> int:
+        """Admission checks of the reference's submit (src/engine/scheduler.rs:389-487)."""
+        request.sampling.validate()
+        vocab = self.engine.spec.vocab_size
+        if not request.prompt:
+            raise ConfigError("the prompt holds no tokens")
+        for t in request.prompt:
+            if not 0 <= int(t) < vocab:
+                raise ConfigError(f"prompt token {t} is outside the vocabulary of {vocab}")
+        deadline = request.deadline_ms if request.deadline_ms is not None else self.config.max_request_ms
+        if not 0 < deadline <= self.config.max_request_ms:
+            raise ConfigError(f"deadline_ms must lie in (0, {self.config.max_request_ms}]")
+        rid = request.request_id if request.request_id is not None else next(self._ids)
+        self.scheduler.submit(rid, len(request.prompt), request.sampling.max_new_tokens)
+        now = time.monotonic()
+        seed = request.sampling.seed if request.sampling.seed is not None else fresh_seed()
+        self._live[rid] = RequestState(request, [int(t) for t in request.prompt], seed, now,
+                                       deadline_at=now + deadline / 1000.0,
+                                       usage=Usage(prompt_tokens=len(request.prompt)))
+        return rid
+
+    def cancel(self, request_id: int) -> None:
+        st = self._live.get(request_id)
+        if st is not None:
+            st.cancelled = True
+
+    def _finish(self, rid: int, reason: str, error: Optional[str] = None) -> None:
+        st = self._live.pop(rid)
+        self.scheduler.finish(rid)
+        st.finish_reason, st.error = reason, error
+        st.usage.completion_tokens = len(st.tokens) - st.usage.prompt_tokens
+        st.usage.elapsed_ms = (time.monotonic() - st.submitted_at) * 1000.0
+        if reason == FINISH_ERROR:
+            self.failed += 1
+        if reason in (FINISH_CANCELLED, FINISH_DEADLINE):
+            self.cancelled += 1
+        self._done[rid] = st
+
+    # ---- the loop ---------------------------------------------------------------------
+    def step(self, on_token: Optional[Callable[[int, int, int], None]] = None) -> bool:
+        """One scheduler turn: interruptions, plan, one engine step, sampling.  False when idle."""
+        now = time.monotonic()
+        for rid, st in list(self._live.items()):      # checked between steps only
+            if st.cancelled:
+                self._finish(rid, FINISH_CANCELLED)
+            elif st.deadline_at is not None and now >= st.deadline_at:
+                self._finish(rid, FINISH_DEADLINE)
+        if not self.scheduler.has_work():
+            return False
+        plan, preempted = self.scheduler.plan()
+        for rid in preempted:
+            self._live[rid].usage.preemptions += 1
+        if not plan:
+            return self.scheduler.has_work() and bool(self._live)
+        entries = []
+        for p in plan:
+            st = self._live[p.request_id]
+            if st.first_step_at is None:
+                st.first_step_at = now
+                st.usage.queue_ms = (now - st.submitted_at) * 1000.0
+            entries.append(StepEntry(p.slot, st.tokens[p.start:p.start + p.count],
+                                     [p.count - 1] if p.want_logits else []))
+        try:
+            logits = self.engine.step(entries)
+        except EngineError as e:
+            for p in plan:                             # src/engine/scheduler.rs:882-895
+                self.scheduler.rollback(p.request_id)
+                self._finish(p.request_id, FINISH_ERROR, str(e))
+            return True
+        sampled = [p for p in plan if p.want_logits]
+        states = [self._live[p.request_id] for p in sampled]
+        tokens = self.sampler.sample(
+            logits, [s.request.sampling for s in states], [s.seed for s in states],
+            [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
+        for p in plan:
+            self.scheduler.advance(p.request_id, p.count)
+        for p, st, tok in zip(sampled, states, tokens):
+            rid = p.request_id
+            if tok in self.eos:                        # the stop token is neither kept nor fed
+                self._finish(rid, FINISH_STOP)
+                continue
+            st.tokens.append(tok)
+            n = self.scheduler.append_token(rid)
+            if on_token is not None:
+                on_token(rid, tok, n - 1)
+            if n >= st.request.sampling.max_new_tokens:
+                self._finish(rid, FINISH_LENGTH)       # no forward for a token nobody will read
+        return True
+
+    def run_until_idle(self, on_token=None) -> None:
+        while self.step(on_token):
+            pass
+
+    def take_result(self, request_id: int) -> Optional[GenerationResult]:
+        st = self._done.pop(request_id, None)
+        if st is None:
+            return None
+        return GenerationResult(request_id, st.generated, st.finish_reason, st.usage, st.error)
+
+    def generate(self, prompts: Sequence[Sequence[int]], sampling: Optional[SamplingParams] = None
+                 ) -> List[GenerationResult]:
+        """Token ids in, token ids out; requests beyond the queue's capacity wait for room."""
+        sampling = sampling or SamplingParams()
+        pending = list(enumerate(prompts))
+        ids: Dict[int, int] = {}
+        while pending or self._live:
+            while pending:
+                if self.scheduler.counters()["queued"] >= self.config.queue_capacity:
+                    break
+                i, prompt = pending[0]
+                try:
+                    ids[i] = self.submit(GenerationRequest(list(prompt), SamplingParams(**vars(sampling))))
+                except ResourceExhausted:
+                    if not self._live:
+                        raise
+                    break
+                pending.pop(0)
+            if not self.step() and pending and not self._live:
+                continue
+        return [self.take_result(ids[i]) for i in range(len(prompts))]
+
+    def metrics(self) -> dict:             # src/engine/scheduler.rs:221-272
+        m = dict(self.scheduler.counters())
+        m["failed"], m["cancelled"] = self.failed, self.cancelled
+        return m

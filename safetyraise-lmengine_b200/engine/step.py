@@ -54,6 +54,7 @@ class Engine:
         self._meta_hosts: list = []          # ring of pinned buffers, each with the event of its last copy
         self._meta_turn = 0
         self.steps_run = 0
+        self.last_h2d_bytes = 0          # bytes of batch layout the last step copied to the device
 
     # ---- construction -----------------------------------------------------
     @classmethod
@@ -193,6 +194,7 @@ class Engine:
         view("slots")[:] = [e.slot for e in entries]
         view("kv_lens")[:] = kv_lens
         dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_h2d_bytes = off * 4
         pair[1] = torch.cuda.Event()
         pair[1].record()
         d = lambda name: dev[sections[name][0]:sections[name][0] + sections[name][1]]

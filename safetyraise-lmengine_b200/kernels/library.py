@@ -42,6 +42,7 @@ def _stream():
 class KernelLibrary:
     def __init__(self):
         self._lib = None
+        self.launches = 0          # kernels launched through this object (a benchmark reports it)
 
     @property
     def lib(self):
@@ -56,6 +57,7 @@ class KernelLibrary:
         return self._lib
 
     def _check(self, status: int, what: str):
+        self.launches += 1
         if status != 0:
             msg = self.lib.srlm_last_error().decode(errors="replace")
             if status < 0:
@@ -141,6 +143,14 @@ class KernelLibrary:
         n, V = logits.shape
         self._check(self.lib.srlm_argmax(_ptr(logits), C.c_longlong(logits.stride(0)), C.c_int(n), C.c_int(V),
                                          _ptr(out_tokens), _ptr(bad_flag), _stream()), "argmax")
+
+    def sample(self, logits, temperature, top_k, top_p, penalty, uniform, history, hist_offsets, out_tokens,
+               bad_flag):
+        n, V = logits.shape
+        self._check(self.lib.srlm_sample(_ptr(logits), C.c_longlong(logits.stride(0)), C.c_int(n), C.c_int(V),
+                                         _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty),
+                                         _ptr(uniform), _ptr(history), _ptr(hist_offsets), _ptr(out_tokens),
+                                         _ptr(bad_flag), _stream()), "sample")
 
 
 ops = KernelLibrary()

@@ -1,0 +1,88 @@
+"""Batch sampler over the logits a step returned: one kernel for all rows.
+
+The random draw of a request's i-th generated token is a function of (seed, i)
+alone, so the same seed gives the same tokens however the requests were batched,
+cut or preempted.  The reference draws from ``rand::StdRng`` seeded per request
+(src/frontend/sampling.rs:72-80); its bit stream is not reproduced, its
+distribution and order of operations are.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    z = x
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def uniform_for(seed: int, index: int) -> float:
+    """A float32 in [0, 1) for the index-th draw of a request with this seed."""
+    bits = _splitmix64(_splitmix64(seed & _MASK) ^ ((index + 1) * 0xD1B54A32D192ED03 & _MASK))
+    return float(np.float32((bits >> 40) * (1.0 / (1 << 24))))
+
+
+def fresh_seed() -> int:
+    return int.from_bytes(os.urandom(8), "little")
+
+
+class Sampler:
+    def __init__(self, device, vocab_size: int, max_rows: int = 64):
+        self.device, self.vocab = device, vocab_size
+        self.bad = torch.zeros(1, dtype=torch.int32, device=device)
+        self._cap = 0
+        self._grow(max_rows)
+
+    def _grow(self, rows: int):
+        if rows <= self._cap:
+            return
+        self._cap = rows
+        self._host = torch.empty(5 * rows, dtype=torch.float32, pin_memory=True)
+        self._dev = torch.empty(5 * rows, dtype=torch.float32, device=self.device)
+        self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               indices: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
+        """logits [n, V] float32 on the device; one token id per row, as Python ints."""
+        n = logits.shape[0]
+        if n == 0:
+            return []
+        self._grow(n)
+        if all(p.is_greedy for p in params):
+            ops.argmax(logits, self._out[:n], self.bad)
+            return self._out[:n].tolist()
+        h = self._host.numpy()
+        c = self._cap
+        for i, p in enumerate(params):
+            h[i] = p.temperature
+            h[c + i] = p.top_p
+            h[2 * c + i] = p.repetition_penalty
+            h[3 * c + i] = uniform_for(seeds[i], indices[i]) if p.temperature > 0 else 0.0
+        h[4 * c:4 * c + n].view(np.int32)[:] = [p.top_k for p in params]
+        # the previous call ended by reading its tokens back, so its copy has left the pinned buffer
+        self._dev.copy_(self._host, non_blocking=True)
+        d = self._dev
+        hist = offs = None
+        if any(p.repetition_penalty != 1.0 for p in params):
+            offsets, flat = [0], []
+            for p, hh in zip(params, histories):
+                if p.repetition_penalty != 1.0:
+                    flat.extend(int(t) for t in hh)
+                offsets.append(len(flat))
+            hist = torch.tensor(flat or [0], dtype=torch.int32, device=self.device)
+            offs = torch.tensor(offsets, dtype=torch.int32, device=self.device)
+        ops.sample(logits, d[:n], d[4 * c:4 * c + n].view(torch.int32), d[c:c + n], d[2 * c:2 * c + n],
+                   d[3 * c:3 * c + n], hist, offs, self._out[:n], self.bad)
+        return self._out[:n].tolist()
