@@ -1,0 +1,413 @@
+// C[M,N] = X[M,K] . W[N,K]^T in bfloat16 with float32 accumulation on the
+// 5th-generation tensor cores: tcgen05.mma reading both operands from shared
+// memory (filled by TMA, 128-byte swizzle) and accumulating in tensor memory.
+//
+// The weight is the MMA's 128-row operand and the tokens are its N side
+// (16..256 wide), so the same kernel serves a decode step of a few tokens and a
+// prefill of thousands: a weight row is read once whatever the batch.  The
+// accumulator tile D[n, m] sits in TMEM with one weight row per lane; the
+// epilogue reads it with tcgen05.ld and writes C[m, n], 32 consecutive n per
+// warp store.  With split-K (grid.z > 1) each split writes its float32 partial
+// tile to a slab of its own in a workspace, and the last split to finish a tile
+// adds the slabs in split order, so the sum is the same on every run.
+//
+// Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the
+// MMAs, warps 2-5 run the epilogue.  Every wait on an mbarrier is bounded: when
+// the bound is hit the kernel raises its error flag and runs to its normal end
+// (TMEM is freed), it never spins for ever.
+//
+// What this replaces in the reference: the naive one-thread-per-output CUDA
+// kernel native/cuda/safetyraise_cuda.cu:43-63 and the CPU loop
+// src/artifact/mod.rs:377-405.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int BM = 128;            // weight rows per tile (MMA M)
+constexpr int BK = 64;             // bf16 elements per k block: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000ll;   // ~2 s: far beyond any real wait
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the flag) if the barrier did not flip in time.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_CYCLES) {
+      atomicExch(err_flag, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (version 1 = Blackwell).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, bits [0,14)
+  d |= (uint64_t)0 << 16;                               // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                               // descriptor version
+  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ uint32_t umma_idesc_bf16_f32(int n) {
+  return (1u << 4)                       // D is float32
+         | (1u << 7) | (1u << 10)        // A and B are bfloat16
+         | ((uint32_t)(n >> 3) << 17)    // N
+         | ((uint32_t)(BM >> 4) << 24);  // M = 128; both operands K-major (bits 15, 16 zero)
+}
+
+template <int COLS>
+__device__ __forceinline__ void tmem_load(uint32_t taddr, uint32_t (&v)[COLS]);
+template <>
+__device__ __forceinline__ void tmem_load<16>(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+template <>
+__device__ __forceinline__ void tmem_load<32>(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+struct GemmArgs {
+  void* C;
+  int c_is_f32;
+  int M, N, K;
+  long long ldc;
+  int* err_flag;
+  int kb_per_split;        // k blocks each split handles
+  float* partial;          // [splits, M, N] float32 (split-K only)
+  int* tile_counters;      // one per output tile, zero on entry (split-K only)
+};
+
+template <int BN>
+constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  // swizzled tiles must start on 1024-byte boundaries
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+  const int total_kb = (args.K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * args.kb_per_split;
+  const int num_kb = min(total_kb, kb_begin + args.kb_per_split) - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES, j = i / STAGES;
+        if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 1)) break;
+        mbar_expect_tx(&full_bar[s], STAGE);
+        uint8_t* a = smem + s * STAGE;
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(a, &map_w, &full_bar[s], k, n0);
+        tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], k, m0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16_f32(BN);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES, j = i / STAGES;
+        ok = mbar_wait(&full_bar[s], j & 1, args.err_flag, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * STAGE);
+        const uint64_t adesc = umma_desc_k_sw128(a_addr), bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 elements further along K inside the swizzle row: 32 bytes, 2 units of 16 bytes
+          tcgen05_mma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+        }
+        tcgen05_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+      }
+      tcgen05_commit(accum_bar);            // arrives when every MMA issued so far is done
+    }
+    __syncwarp();
+  } else {
+    const bool ok = mbar_wait(accum_bar, 0, args.err_flag, 3);
+    tcgen05_fence_after();
+    const int lane_base = 32 * (warp & 3);              // the TMEM lanes this warp may read
+    const int n = n0 + lane_base + lane;
+    constexpr int CH = BN < 32 ? 16 : 32;
+    const bool split = gridDim.z > 1;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CH) {
+        uint32_t v[CH];
+        tmem_load<CH>(tmem_base + ((uint32_t)lane_base << 16) + c, v);
+        tmem_load_wait();
+        if (n < args.N) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int m = m0 + c + j;
+            if (m < args.M) {
+              const float x = __uint_as_float(v[j]);
+              const size_t at = (size_t)m * args.ldc + n;
+              if (split) args.partial[((size_t)blockIdx.z * args.M + m) * args.N + n] = x;
+              else if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x;
+              else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x);
+            }
+          }
+        }
+      }
+    }
+    if (split) {
+      // the last split to finish this tile adds the partials in split order (the same order on
+      // every run) and writes the result
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const int prev = atomicAdd(&args.tile_counters[tile], 1);
+        *last_flag = (prev == (int)gridDim.z - 1);
+        if (*last_flag) args.tile_counters[tile] = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag && n < args.N) {
+        __threadfence();
+        for (int j = 0; j < BN; ++j) {
+          const int m = m0 + j;
+          if (m >= args.M) break;
+          float x = 0.f;
+          for (int z = 0; z < (int)gridDim.z; ++z)
+            x += __ldcg(&args.partial[((size_t)z * args.M + m) * args.N + n]);
+          const size_t at = (size_t)m * args.ldc + n;
+          if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x;
+          else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps and launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows, K] bfloat16 row-major with leading dimension ld; box = [box_rows, 64]
+static bool make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows,
+                     bool weight) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  weight ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void* ptr; long long rows, K, ld; int box_rows;
+  bool operator<(const MapKey& o) const {
+    return std::tie(ptr, rows, K, ld, box_rows) < std::tie(o.ptr, o.rows, o.K, o.ld, o.box_rows);
+  }
+};
+static std::map<MapKey, CUtensorMap> g_maps;
+static std::mutex g_maps_mutex;
+
+static const CUtensorMap* cached_map(const void* ptr, long long rows, long long K, long long ld, int box_rows,
+                                     bool weight) {
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  MapKey key{ptr, rows, K, ld, box_rows};
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    if (!make_map(&m, ptr, rows, K, ld, box_rows, weight)) return nullptr;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  return &it->second;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, int splits, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * stage_bytes<BN>() + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return refuse((int)e, "gemm_tcgen05: cannot get %d bytes of shared memory", SMEM);
+    configured = true;
+  }
+  dim3 grid((a.N + BM - 1) / BM, (a.M + BN - 1) / BN, splits);
+  gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, SMEM, stream>>>(*mw, *mx, a);
+  return launched();
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+// workspace (only when splits > 1): one int per output tile, zero on entry and left zero on exit,
+// at the start; float32 partials [splits, M, N] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
+extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                    long long ldx, long long ldw, long long ldc, int splits, void* workspace,
+                                    long long workspace_bytes, int* err_flag, cudaStream_t stream) {
+  if (M <= 0) return ST_OK;
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < N)
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
+  if (K % 8 || ldx % 8 || ldw % 8)
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05: K=%d and the leading dimensions must be multiples of 8 "
+                  "(TMA rows start on 16-byte boundaries)", K);
+  if (((uintptr_t)X | (uintptr_t)W) & 15)
+    return refuse(ST_BAD_ALIGN, "gemm_tcgen05: operands must be 16-byte aligned");
+  if (c_dtype != DT_F32 && c_dtype != DT_BF16) return refuse(ST_BAD_DTYPE, "gemm_tcgen05: output dtype %d", c_dtype);
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > total_kb) splits = total_kb;
+  int kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr};
+  if (splits > 1) {
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+    const long long need = 65536 + (long long)splits * M * N * 4;
+    if (!workspace || workspace_bytes < need || tiles * 4 > 65536)
+      return refuse(ST_BAD_SIZE, "gemm_tcgen05: split-K with %d splits needs %lld bytes of workspace, got %lld",
+                    splits, need, workspace_bytes);
+    a.tile_counters = reinterpret_cast<int*>(workspace);
+    a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 65536);
+  }
+  const CUtensorMap* mw = cached_map(W, N, K, ldw, BM, true);
+  const CUtensorMap* mx = cached_map(X, M, K, ldx, bn, false);
+  if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
+  switch (bn) {
+    case 16: return launch<16, 10>(mw, mx, a, splits, stream);
+    case 32: return launch<32, 8>(mw, mx, a, splits, stream);
+    case 64: return launch<64, 8>(mw, mx, a, splits, stream);
+    case 128: return launch<128, 6>(mw, mx, a, splits, stream);
+    default: return launch<256, 4>(mw, mx, a, splits, stream);
+  }
+}

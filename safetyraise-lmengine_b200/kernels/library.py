@@ -43,6 +43,7 @@ class KernelLibrary:
     def __init__(self):
         self._lib = None
         self.launches = 0          # kernels launched through this object (a benchmark reports it)
+        self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
 
     @property
     def lib(self):
@@ -128,9 +129,62 @@ class KernelLibrary:
             C.c_int(M), C.c_int(N), C.c_int(K), C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)),
             C.c_longlong(out.stride(0)), _stream()), "gemm_tn_simt")
 
+    # split-K workspace of the tensor-core GEMM: 64 KiB of tile counters, then float32 partials
+    GEMM_WS_BYTES = 65536 + (64 << 20)
+
+    def _gemm_state(self, device):
+        st = getattr(self, "_gemm_ws", None)
+        if st is None or st[0].device != device:
+            ws = torch.zeros(self.GEMM_WS_BYTES, dtype=torch.uint8, device=device)
+            err = torch.zeros(1, dtype=torch.int32, device=device)
+            st = self._gemm_ws = (ws, err)
+        return st
+
+    def gemm_error_flag(self, device) -> int:
+        """Nonzero if a tensor-core GEMM gave up on a wait since the flag was last read (synchronises)."""
+        err = self._gemm_state(device)[1]
+        v = int(err.item())
+        if v:
+            err.zero_()
+        return v
+
+    @staticmethod
+    def gemm_splits(M: int, N: int, K: int) -> int:
+        """How many ways to split K so that a skinny product still fills the 148 SMs."""
+        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
+        total_kb = (K + 63) // 64
+        if tiles >= 120:
+            return 1
+        splits = max(1, min(148 // tiles, total_kb // 4, 16))
+        while splits > 1 and 65536 + splits * M * N * 4 > KernelLibrary.GEMM_WS_BYTES:
+            splits -= 1
+        return splits
+
+    def gemm_tn_tcgen05(self, a, w, out, splits=None):
+        """out[M,N] = a[M,K] @ w[N,K]^T, bfloat16 operands, tcgen05 tensor cores, float32 accumulation."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise ShapeError(f"gemm_tcgen05: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, "
+                             f"out {tuple(out.shape)}")
+        ws, err = self._gemm_state(a.device)
+        if splits is None:
+            splits = self.gemm_splits(M, N, K)
+        self._check(self.lib.srlm_gemm_tn_tcgen05(
+            _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
+            C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), C.c_int(splits),
+            _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), _stream()), "gemm_tn_tcgen05")
+
     def gemm(self, a, w, out):
-        """The product path's matrix product: picks the kernel for the dtypes and sizes."""
-        self.gemm_tn_simt(a, w, out)
+        """The product path's matrix product: picks the kernel for the dtypes and sizes.  bfloat16
+        operands go to the tensor cores; float32 operands, and widths that TMA cannot address
+        (K not a multiple of 8), go to the float32 FMA kernel."""
+        if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+                and not self.force_simt_gemm):
+            self.gemm_tn_tcgen05(a, w, out)
+        else:
+            self.gemm_tn_simt(a, w, out)
 
     def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
                         window=0):

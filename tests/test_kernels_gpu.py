@@ -264,3 +264,50 @@ def test_argmax_ties_go_to_the_lowest_id():
     big[1, 7] = float("nan")
     ops().argmax(big, out3, bad)
     assert bad.item() == 1
+
+
+@pytest.mark.parametrize("M, N, K, splits", [
+    (1, 128, 64, 1), (8, 384, 96, 1), (16, 192, 64, 1), (17, 200, 72, 1), (33, 4096, 4096, 4),
+    (64, 2560, 4096, 1), (64, 512, 1024, 3), (100, 384, 256, 1), (129, 640, 512, 2), (300, 640, 520, 1),
+    (2048, 1024, 512, 1), (5, 6144, 4096, None), (8, 4096, 12288, None), (257, 128, 8, 1)])
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
+def test_gemm_tn_tcgen05(M, N, K, splits, odt):
+    g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, generator=g).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+    ops().gemm_tn_tcgen05(a, w, out, splits=splits)
+    assert ops().gemm_error_flag(a.device) == 0
+    ref = a.double() @ w.double().T
+    if odt == torch.float32:
+        assert torch.allclose(out.double(), ref, rtol=1e-4, atol=2e-4 * math.sqrt(K))
+        twin = torch.empty(M, N, device=DEV)
+        ops().gemm_tn_simt(a, w, twin)
+        assert torch.allclose(out, twin, rtol=1e-4, atol=2e-4 * math.sqrt(K))
+    else:
+        assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    # twice in a row: the split-K counters were left clean
+    out2 = torch.empty_like(out)
+    ops().gemm_tn_tcgen05(a, w, out2, splits=splits)
+    assert torch.equal(out, out2)
+
+
+def test_gemm_tcgen05_finds_each_k_and_row():
+    """Identity-like operands: a misplaced row, column or k block shows as a wrong integer."""
+    K, N, M = 256, 256, 40
+    w = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
+    w[torch.arange(N), torch.arange(N) % K] = 1.0
+    a = (torch.arange(M * K, device=DEV).reshape(M, K) % 251).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    ops().gemm_tn_tcgen05(a, w, out, splits=1)
+    assert torch.equal(out, a.float()[:, torch.arange(N, device=DEV) % K])
+
+
+def test_gemm_tcgen05_refuses_what_tma_cannot_address():
+    from safetyraise_lmengine_b200.errors import ShapeError
+    a = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(8, 100, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros(4, 8, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ShapeError):
+        ops().gemm_tn_tcgen05(a, w, out)
+    ops().gemm(a, w, out)              # the dispatcher falls back to the FMA kernel for such a width
