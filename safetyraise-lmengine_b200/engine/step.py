@@ -206,7 +206,7 @@ class Engine:
             kv_slot={g.name: d("kv_slot:" + g.name) for g in groups},
             host={"q_lens": q_lens, "starts": starts, "kv_lens": kv_lens, "slots": [e.slot for e in entries]},
             cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens), kv_bound=pages * ps)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""

@@ -44,6 +44,7 @@ class KernelLibrary:
         self._lib = None
         self.launches = 0          # kernels launched through this object (a benchmark reports it)
         self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
+        self.force_simt_attention = False
 
     @property
     def lib(self):
@@ -186,11 +187,60 @@ class KernelLibrary:
         else:
             self.gemm_tn_simt(a, w, out)
 
+    def paged_attention_rows(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv, hd,
+                             page_size, scale, window=0):
+        """bfloat16 tensor-core attention for a ragged batch; work: int32 [n, 2] (entry, tile of 64 rows)."""
+        self._check(self.lib.srlm_paged_attention_rows(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), C.c_int(block_table.stride(0)),
+            _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]), C.c_int(nq), C.c_int(nkv), C.c_int(hd),
+            C.c_int(page_size), C.c_float(scale), C.c_int(window or 0), _stream()), "paged_attention_rows")
+
+    def paged_attention_keys(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv, hd,
+                             page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
+        """bfloat16 tensor-core attention when every entry has at most 16 rows (decode); keys in nsplit slices."""
+        self._check(self.lib.srlm_paged_attention_keys(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), C.c_int(block_table.stride(0)),
+            _ptr(cu_q), _ptr(kv_lens), C.c_int(n_entries), C.c_int(nq), C.c_int(nkv), C.c_int(hd),
+            C.c_int(page_size), C.c_float(scale), C.c_int(window or 0), C.c_int(kv_chunk), C.c_int(nsplit),
+            _ptr(part_o), _ptr(part_ml), _stream()), "paged_attention_keys")
+
+    @staticmethod
+    def attention_split(n_entries: int, nkv: int, max_kv: int):
+        """(nsplit, kv_chunk) for the keys-split kernel: enough blocks to fill the GPU, slices of whole tiles."""
+        tiles = max(1, (max_kv + 63) // 64)
+        nsplit = max(1, min(tiles, -(-296 // max(1, n_entries * nkv)), 32))
+        chunk = -(-tiles // nsplit) * 64
+        nsplit = -(-tiles * 64 // chunk)
+        return nsplit, chunk
+
     def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
                         window=0):
-        """The product path's attention over the cache for the batch of ``ctx``."""
-        self.paged_attention_simt(q, k_cache, v_cache, out, block_table, ctx.entry_of_token, ctx.positions,
-                                  nq, nkv, hd, page_size, scale, window)
+        """The product path's attention over the cache for the batch of ``ctx``: tensor cores for
+        bfloat16 (keys-split when every entry is a few rows, rows-split otherwise), float32 FMA for
+        the float32 path."""
+        if q.dtype != torch.bfloat16 or hd % 16 or hd > 256 or self.force_simt_attention:
+            self.paged_attention_simt(q, k_cache, v_cache, out, block_table, ctx.entry_of_token, ctx.positions,
+                                      nq, nkv, hd, page_size, scale, window)
+            return
+        g = nq // nkv
+        if ctx.max_q_len * g <= 16:
+            nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
+            part_o = part_ml = None
+            if nsplit > 1:
+                part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,
+                                           reserve=0)
+                part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2, torch.float32,
+                                            reserve=0)
+            self.paged_attention_keys(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries,
+                                      nq, nkv, hd, page_size, scale, window, chunk, nsplit, part_o, part_ml)
+            return
+        work = ctx.tables.get(("attention_rows_work", g))
+        if work is None:
+            pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"]) for t in range((ql * g + 63) // 64)]
+            work = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(q.device, non_blocking=True)
+            ctx.tables[("attention_rows_work", g)] = work
+        self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq, nkv, hd,
+                                  page_size, scale, window)
 
     # ---- sampling -------------------------------------------------------------
     def argmax(self, logits, out_tokens, bad_flag):

@@ -118,6 +118,7 @@ class StepContext:
     tables: dict = field(default_factory=dict)    # position-encoding tables of this step
     max_q_len: int = 1
     max_kv_len: int = 1
+    kv_bound: int = 1                         # an upper bound of max_kv_len that kernels may size their grids by
 
 
 class Part:

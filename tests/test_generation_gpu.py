@@ -97,7 +97,7 @@ def test_stop_token_cancel_deadline_and_queue(folder_b):
     a = llm.submit(GenerationRequest(prompt * 6, SamplingParams(temperature=0.0, max_new_tokens=4)))
     b = llm.submit(GenerationRequest(prompt, SamplingParams(temperature=0.0, max_new_tokens=4), deadline_ms=1))
     with pytest.raises(ResourceExhausted):
-        llm.submit(GenerationRequest(prompt)), llm.submit(GenerationRequest(prompt))
+        llm.submit(GenerationRequest(prompt, SamplingParams(max_new_tokens=4))), llm.submit(GenerationRequest(prompt, SamplingParams(max_new_tokens=4)))
     llm.step()
     llm.cancel(a)
     import time

@@ -311,3 +311,72 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     with pytest.raises(ShapeError):
         ops().gemm_tn_tcgen05(a, w, out)
     ops().gemm(a, w, out)              # the dispatcher falls back to the FMA kernel for such a width
+
+
+ATT_CASES = [(4, 2, 16, 4), (6, 1, 32, 16), (32, 8, 128, 16), (5, 5, 80, 8), (2, 1, 256, 32), (8, 2, 64, 16),
+             (12, 4, 112, 16)]
+
+
+@pytest.mark.parametrize("nq, nkv, hd, ps", ATT_CASES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_paged_attention_rows_mma(nq, nkv, hd, ps, window):
+    lens_q, lens_kv = [1, 7, 33, 1, 2, 150], [1, 40, 33, 65, 100, 300]
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=160)
+    g = nq // nkv
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    work = torch.tensor([(e, t) for e, ql in enumerate(lens_q) for t in range((ql * g + 63) // 64)],
+                        dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_rows(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, scale, window)
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
+    twin = torch.empty_like(q)
+    ops().paged_attention_simt(q, kc, vc, twin, bt, eot, pos, nq, nkv, hd, ps, scale, window)
+    assert torch.allclose(out.float(), twin.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nq, nkv, hd, ps", ATT_CASES)
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("nsplit", [1, 3])
+def test_paged_attention_keys_mma(nq, nkv, hd, ps, window, nsplit):
+    g = nq // nkv
+    ql = max(1, min(3, 16 // g))
+    lens_q, lens_kv = [1, ql, 1, 1, ql], [1, 40, 65, 300, 129]
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=160)
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    n = len(lens_q)
+    chunk = ((max(lens_kv) + nsplit - 1) // nsplit + 63) // 64 * 64
+    part_o = torch.full((n * nkv * nsplit * 16, hd), float("nan"), device=DEV)
+    part_ml = torch.full((n * nkv * nsplit * 16, 2), float("nan"), device=DEV)
+    out = torch.full_like(q, float("nan"))
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_keys(q, kc, vc, out, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
+                               part_o, part_ml)
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("kernel", ["rows", "keys"])
+def test_mma_attention_finds_one_far_key(kernel):
+    nq, nkv, hd, ps = 8, 2, 64, 16
+    for far in (0, 63, 64, 333, 699):
+        q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, [1], [700], pages=48)
+        kc = kc * 0.01
+        page, off = tables[0][far // ps], far % ps
+        kc[page, off] = q.view(nq, hd)[0::4] * 4.0                 # heads 0 and 4 -> kv heads 0 and 1
+        out = torch.empty_like(q)
+        cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+        kvl = torch.tensor([700], dtype=torch.int32, device=DEV)
+        if kernel == "rows":
+            work = torch.tensor([[0, 0]], dtype=torch.int32, device=DEV)
+            ops().paged_attention_rows(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, 1.0, 0)
+        else:
+            part_o = torch.empty(2 * 4 * 16, hd, device=DEV)
+            part_ml = torch.empty(2 * 4 * 16, 2, device=DEV)
+            ops().paged_attention_keys(q, kc, vc, out, bt, cu, kvl, 1, nq, nkv, hd, ps, 1.0, 0, 192, 4, part_o, part_ml)
+        got = out.float().view(nq, hd)
+        for h, kh in ((0, 0), (4, 1)):
+            assert torch.allclose(got[h], vc[page, off, kh].float(), atol=2e-2), (far, h)
