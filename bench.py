@@ -103,7 +103,7 @@ def reference_arm():
     return 0
 
 
-def build_engine(layers: int, max_requests: int, tokens_in_cache: int, max_batch_tokens: int):
+def build_engine(layers: int, max_requests: int, tokens_in_cache: int, max_batch_tokens: int, graphs=True):
     import torch
     from safetyraise_lmengine_b200 import Engine, spec_from_config
     from safetyraise_lmengine_b200.parts.model import tensor_decls
@@ -113,7 +113,8 @@ def build_engine(layers: int, max_requests: int, tokens_in_cache: int, max_batch
     src = RandomWeights(tensor_decls(spec), seed=0, device="cuda:0")
     num_pages = (tokens_in_cache + PAGE_SIZE - 1) // PAGE_SIZE + max_requests
     eng = Engine.from_source(cfg, src, dtype="bfloat16", page_size=PAGE_SIZE, num_pages=num_pages,
-                             max_requests=max_requests, max_batch_tokens=max_batch_tokens, max_context=4096)
+                             max_requests=max_requests, max_batch_tokens=max_batch_tokens, max_context=4096,
+                             options={"cuda_graphs": graphs})
     torch.cuda.synchronize()
     return eng
 
@@ -253,6 +254,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-extras", action="store_true", help="only the default decode measurement")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -267,7 +269,7 @@ def main() -> int:
     B = args.batch
     big = max(64, B)
     eng = build_engine(args.layers, max_requests=big, tokens_in_cache=big * (CONTEXT + 256) + PREFILL_TOKENS,
-                       max_batch_tokens=PREFILL_TOKENS)
+                       max_batch_tokens=PREFILL_TOKENS, graphs=not args.no_graphs)
     slots = fill_contexts(eng, B, CONTEXT)
     with ClockSampler() as clocks:
         ms, launches = time_decode(eng, slots, args.steps, args.warmup)

@@ -104,7 +104,8 @@ class CacheManager:
             arr([g.window or 0 for g in self._paged]))
         if not self._h:
             raise ConfigError("the cache manager refused its configuration")
-        # device memory: per paged group [entries, 2, num_pages, page_size, kv_heads, head_dim]
+        # device memory: per paged group [entries, 2, num_pages, kv_heads, page_size, head_dim]:
+        # one KV head's share of a page is contiguous, which is what the attention kernels stream
         self.kv_pools: Dict[str, torch.Tensor] = {}
         self.state_pools: Dict[str, torch.Tensor] = {}
         self.entry_home: Dict[int, Tuple[str, int]] = {}
@@ -119,7 +120,7 @@ class CacheManager:
                 self.state_pools[g.name] = torch.zeros((len(g.entries), max_requests) + tuple(g.state_shape),
                                                        dtype=g.state_dtype, device=device)
             else:
-                self.kv_pools[g.name] = torch.zeros((len(g.entries), 2, num_pages, page_size, g.kv_heads,
+                self.kv_pools[g.name] = torch.zeros((len(g.entries), 2, num_pages, g.kv_heads, page_size,
                                                      g.head_dim), dtype=dtype, device=device)
         self._table_buf = (C.c_int32 * (num_pages + 1))()
 
@@ -194,7 +195,7 @@ class CacheManager:
 
     # ---- device views ---------------------------------------------------------
     def kv_of_entry(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor, str]:
-        """(K pool, V pool, group name) of one cache entry: [num_pages, page_size, kv_heads, head_dim]."""
+        """(K pool, V pool, group name) of one cache entry: [num_pages, kv_heads, page_size, head_dim]."""
         name, i = self.entry_home[entry]
         pool = self.kv_pools[name]
         return pool[i, 0], pool[i, 1], name

@@ -1,0 +1,461 @@
+// Decode attention over the paged cache with TMA: at most 16 rows (query tokens
+// x query heads of one KV group) per entry and KV head, keys in slices.
+//
+// A block takes one entry, one KV head and one slice of the keys.  One producer
+// thread walks the block table and brings whole pages in with tiled TMA copies
+// (a KV head's share of a page is one contiguous [page_size, head_dim] block of
+// the cache), 128-byte swizzled, into a ring of stages guarded by mbarriers.
+// Four consumer warps each compute the scores of all 64 keys of a tile
+// (mma.sync m16n8k16, float32 accumulation) and the online softmax, and each
+// accumulates one quarter of the head dimension of P.V, so nothing is merged
+// between warps.  Slices are merged by whichever block of an (entry, KV head)
+// finishes last, in slice order.  Every wait is bounded: when a bound is hit the
+// block raises the error flag and leaves.
+//
+// Taken when head_dim is a multiple of 64 and page_size is 8, 16, 32 or a
+// multiple of 64; other sizes use the cp.async kernel in attention_mma.cu.
+// Formula: src/model/math.rs:102-155.
+#include <cuda.h>
+#include <math_constants.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace srlm {
+namespace dec {
+
+constexpr int KT = 64;
+constexpr int STAGES = 3;
+constexpr int CONSUMERS = 4;
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr long long WAIT_CYCLES = 4000000000ll;
+
+struct Args {
+  const bf16* q;
+  bf16* out;
+  const int* block_table;
+  int table_stride;
+  const int* cu_q;
+  const int* kv_lens;
+  int nq, nkv, hd, page_size;
+  float scale_log2;
+  int window;
+  int kv_chunk, nsplit;
+  float* part_o;
+  float* part_ml;
+  int* slice_counters;
+  int* err_flag;
+};
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(s32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > WAIT_CYCLES) {
+      atomicExch(err_flag, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Address of the 16-byte chunk `chunk16` (of head_dim/8) of key `key` in a tile made of panels of
+// 64 dims: [panel][64 keys][128 bytes], 128-byte swizzle (chunk ^= key & 7).
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int key, int chunk16) {
+  return tile + (uint32_t)(chunk16 >> 3) * (KT * 128) + (uint32_t)key * 128 +
+         (uint32_t)(((chunk16 & 7) ^ (key & 7)) << 4);
+}
+
+template <int HD>     // 64, 128, 192 or 256
+__global__ void __launch_bounds__(THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const Args a) {
+  constexpr int PANELS = HD / 64;
+  constexpr int TILE_BYTES = KT * HD * 2;            // one K or V tile
+  constexpr int KS = HD / 16;                        // k steps of Q.K^T
+  constexpr int NT_O = HD / 8 / CONSUMERS;           // output n-tiles per consumer warp
+  extern __shared__ uint8_t dec_smem_raw[];
+  uint8_t* smem = dec_smem_raw + ((1024u - (s32(dec_smem_raw) & 1023u)) & 1023u);
+  uint8_t* tiles = smem;                                              // [STAGES][K tile | V tile]
+  bf16* q_s = reinterpret_cast<bf16*>(smem + STAGES * 2 * TILE_BYTES);  // [16][HD + 8]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(q_s + 16 * (HD + 8));
+  uint64_t* empty_bar = full_bar + STAGES;
+  __shared__ int is_last;
+
+  const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
+  const int g = a.nq / a.nkv;
+  const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
+  const int rows_total = q_len * g;
+  const int* table = a.block_table + (size_t)e * a.table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int first_key = a.window > 0 ? max(0, start - a.window + 1) : 0;
+  const int slice_lo = z * a.kv_chunk, slice_hi = min(kv_len, slice_lo + a.kv_chunk);
+  const int jb0 = max(slice_lo, (first_key / KT) * KT);
+  const int n_tiles = slice_hi > jb0 ? (slice_hi - jb0 + KT - 1) / KT : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CONSUMERS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // Q rows -> shared memory (plain loads: 16 rows at most)
+  for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
+    const int row = idx / (HD / 8), c = idx % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows_total)
+      v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * (HD + 8) + c * 8) = v;
+  }
+  __syncthreads();
+
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  if (warp == CONSUMERS) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int ps = a.page_size;
+      const int box_rows = ps < KT ? ps : KT;          // keys per TMA copy
+      const int boxes = KT / box_rows;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % STAGES, j = t / STAGES;
+        if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, a.err_flag, 11)) break;
+        mbar_expect_tx(&full_bar[s], 2 * TILE_BYTES);
+        uint8_t* kt = tiles + s * 2 * TILE_BYTES;
+        uint8_t* vt = kt + TILE_BYTES;
+        const int jb = jb0 + t * KT;
+        for (int b = 0; b < boxes; ++b) {
+          const int key = jb + b * box_rows;
+          const int pg = key / ps;
+          // beyond the request's pages (keys that no row sees): any valid page will do, they are masked
+          const int page = (pg < a.table_stride && key < kv_len) ? max(table[pg], 0) : 0;
+          const int row = (page * a.nkv + kvh) * ps + key % ps;      // row of the [pages*nkv*ps, HD] view
+#pragma unroll
+          for (int p = 0; p < PANELS; ++p) {
+            tma_load_2d(kt + p * (KT * 128) + b * box_rows * 128, &map_k, &full_bar[s], p * 64, row);
+            tma_load_2d(vt + p * (KT * 128) + b * box_rows * 128, &map_v, &full_bar[s], p * 64, row);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- consumers ----------------
+    uint32_t qf[KS][4];
+    {
+      const int mi = lane >> 3;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int row = (mi & 1) * 8 + (lane & 7);
+        ldsm4(qf[ks], s32(q_s + row * (HD + 8) + (ks * 2 + (mi >> 1)) * 8));
+      }
+    }
+    const int ra = lane >> 2, rb = ra + 8;
+    const int pos0 = start + min(ra, rows_total - 1) / g, pos1 = start + min(rb, rows_total - 1) / g;
+    const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+    const int mi = lane >> 3;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int s = t % STAGES, j = t / STAGES;
+      ok = mbar_wait(&full_bar[s], j & 1, a.err_flag, 12);
+      if (!ok) break;
+      const uint32_t kt = s32(tiles + s * 2 * TILE_BYTES), vt = kt + TILE_BYTES;
+      const int jb = jb0 + t * KT;
+      // scores of all 64 keys
+      float sc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int nt = 0; nt < 8; nt += 2) {
+          uint32_t b[4];
+          ldsm4(b, tile_addr(kt, (nt + (mi >> 1)) * 8 + (lane & 7), ks * 2 + (mi & 1)));
+          mma16816(sc[nt], qf[ks], b[0], b[1]);
+          mma16816(sc[nt + 1], qf[ks], b[2], b[3]);
+        }
+      }
+      const bool need_mask = jb + KT > min(slice_hi, start + 1) || a.window > 0;
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float v = sc[nt][x] * a.scale_log2;
+          if (need_mask) {
+            const int key = jb + nt * 8 + (lane & 3) * 2 + (x & 1);
+            const int pos = x < 2 ? pos0 : pos1, lo = x < 2 ? lo0 : lo1;
+            if (key > pos || key < lo || key >= slice_hi) v = -CUDART_INF_F;
+          }
+          sc[nt][x] = v;
+          if (x < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float base0 = mn0 == -CUDART_INF_F ? 0.f : mn0, base1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);
+      m0 = mn0;
+      m1 = mn1;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pf[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const float p0 = exp2f(sc[nt][0] - base0), p1 = exp2f(sc[nt][1] - base0);
+        const float p2 = exp2f(sc[nt][2] - base1), p3 = exp2f(sc[nt][3] - base1);
+        sum0 += p0 + p1;
+        sum1 += p2 + p3;
+        pf[nt >> 1][(nt & 1) * 2 + 0] = pack2(p0, p1);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p2, p3);
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * alpha0 + sum0;
+      l1 = l1 * alpha1 + sum1;
+#pragma unroll
+      for (int dn = 0; dn < NT_O; ++dn) {
+        o[dn][0] *= alpha0; o[dn][1] *= alpha0; o[dn][2] *= alpha1; o[dn][3] *= alpha1;
+      }
+      // rows of the V tile that no query sees (past the sequence's end in its last tile, before the
+      // window's start in its first) may hold anything: a zero weight times a non-finite value would
+      // still poison the sum, so those rows of this warp's dims are cleared
+      {
+        const int bad_from = jb + KT > kv_len ? kv_len - jb : KT;             // rows [bad_from, KT)
+        const int bad_to = (a.window > 0 && jb < first_key) ? first_key - jb : 0;   // rows [0, bad_to)
+        if (bad_from < KT || bad_to > 0) {
+          for (int idx = lane; idx < KT * NT_O; idx += 32) {
+            const int key = idx / NT_O, c16 = warp * NT_O + idx % NT_O;
+            if (key >= bad_from || key < bad_to)
+              asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(tile_addr(vt, key, c16)), "r"(0) : "memory");
+          }
+          __syncwarp();
+        }
+      }
+      // O[:, this warp's dims] += P . V
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+        for (int dn = 0; dn < NT_O; dn += 2) {
+          uint32_t b[4];
+          ldsm4_t(b, tile_addr(vt, kk * 16 + (mi & 1) * 8 + (lane & 7), warp * NT_O + dn + (mi >> 1)));
+          mma16816(o[dn], pf[kk], b[0], b[1]);
+          mma16816(o[dn + 1], pf[kk], b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+  }
+
+  // ---------------- output ----------------
+  const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
+  if (warp < CONSUMERS) {
+    const int ra = lane >> 2, rb = ra + 8;
+#pragma unroll
+    for (int dn = 0; dn < NT_O; ++dn) {
+      const int d = (warp * NT_O + dn) * 8 + (lane & 3) * 2;
+      if (a.nsplit == 1) {
+        if (ra < rows_total) {
+          const float inv = l0 > 0.f ? 1.f / l0 : 0.f;
+          *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + ra / g) * a.nq + kvh * g + ra % g) * HD + d) =
+              pack2(o[dn][0] * inv, o[dn][1] * inv);
+        }
+        if (rb < rows_total) {
+          const float inv = l1 > 0.f ? 1.f / l1 : 0.f;
+          *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + rb / g) * a.nq + kvh * g + rb % g) * HD + d) =
+              pack2(o[dn][2] * inv, o[dn][3] * inv);
+        }
+      } else {
+        if (ra < rows_total)
+          *reinterpret_cast<float2*>(a.part_o + ((slab0 + z) * 16 + ra) * HD + d) = make_float2(o[dn][0], o[dn][1]);
+        if (rb < rows_total)
+          *reinterpret_cast<float2*>(a.part_o + ((slab0 + z) * 16 + rb) * HD + d) = make_float2(o[dn][2], o[dn][3]);
+      }
+    }
+    if (a.nsplit > 1 && warp == 0 && (lane & 3) == 0) {
+      if (ra < rows_total) *reinterpret_cast<float2*>(a.part_ml + ((slab0 + z) * 16 + ra) * 2) = make_float2(m0, l0);
+      if (rb < rows_total) *reinterpret_cast<float2*>(a.part_ml + ((slab0 + z) * 16 + rb) * 2) = make_float2(m1, l1);
+    }
+  }
+  if (a.nsplit == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = a.slice_counters + e * a.nkv + kvh;
+    const int prev = atomicAdd(counter, 1);
+    is_last = prev == a.nsplit - 1;
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows_total * HD; idx += THREADS) {
+    const int row = idx / HD, d = idx - row * HD;
+    float mm = -CUDART_INF_F;
+    for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]));
+    const float base = mm == -CUDART_INF_F ? 0.f : mm;
+    float ll = 0.f, oo = 0.f;
+    for (int s = 0; s < a.nsplit; ++s) {
+      const float f = exp2f(__ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]) - base);
+      ll += __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2 + 1]) * f;
+      oo += __ldcg(&a.part_o[((slab0 + s) * 16 + row) * HD + d]) * f;
+    }
+    a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+struct Key {
+  const void* ptr; long long rows; int hd, box_rows;
+  bool operator<(const Key& o) const { return std::tie(ptr, rows, hd, box_rows) < std::tie(o.ptr, o.rows, o.hd, o.box_rows); }
+};
+static std::map<Key, CUtensorMap> g_maps;
+static std::mutex g_mutex;
+
+// the cache as a matrix [rows = pages * kv_heads * page_size, head_dim]; box = [box_rows, 64 dims]
+static const CUtensorMap* cache_map(const void* ptr, long long rows, int hd, int box_rows) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Key key{ptr, rows, hd, box_rows};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) return &it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return nullptr;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  if (g_maps.size() > 4096) g_maps.clear();
+  return &g_maps.emplace(key, m).first->second;
+}
+
+template <int HD>
+static int launch(const CUtensorMap* mk, const CUtensorMap* mv, const Args& a, int n_entries, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * 2 * KT * HD * 2 + 16 * (HD + 8) * 2 + 2 * STAGES * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (err != cudaSuccess) return refuse((int)err, "attention_decode_tma: cannot get %d bytes of shared memory", SMEM);
+    configured = true;
+  }
+  attention_decode_tma_kernel<HD><<<dim3(n_entries, a.nkv, a.nsplit), THREADS, SMEM, stream>>>(*mk, *mv, a);
+  return launched();
+}
+
+}  // namespace dec
+}  // namespace srlm
+
+using namespace srlm;
+
+// 1 if srlm_paged_attention_decode_tma takes these sizes.
+extern "C" int srlm_attention_decode_tma_takes(int hd, int page_size) {
+  const bool hd_ok = hd == 64 || hd == 128 || hd == 192 || hd == 256;
+  const bool ps_ok = page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0);
+  return hd_ok && ps_ok;
+}
+
+// Same contract as srlm_paged_attention_keys (attention_mma.cu); num_pages is the pool's page count.
+extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                               long long num_pages, const int* block_table, int table_stride,
+                                               const int* cu_q, const int* kv_lens, int n_entries, int nq, int nkv,
+                                               int hd, int page_size, float scale, int window, int kv_chunk,
+                                               int nsplit, float* part_o, float* part_ml, int* slice_counters,
+                                               int* err_flag, cudaStream_t stream) {
+  if (n_entries <= 0) return ST_OK;
+  if (!srlm_attention_decode_tma_takes(hd, page_size) || nq <= 0 || nkv <= 0 || nq % nkv)
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
+  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % dec::KT || (nsplit > 1 && (!part_o || !part_ml || !slice_counters)))
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
+  if (nsplit > 65535 || nkv > 65535) return refuse(ST_BAD_SIZE, "attention_decode_tma: grid too large");
+  const int box_rows = page_size < dec::KT ? page_size : dec::KT;
+  const long long rows = num_pages * nkv * page_size;
+  const CUtensorMap* mk = dec::cache_map(k_cache, rows, hd, box_rows);
+  const CUtensorMap* mv = dec::cache_map(v_cache, rows, hd, box_rows);
+  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
+  dec::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, nq, nkv, hd, page_size,
+              scale * 1.4426950408889634f, window, kv_chunk, nsplit, part_o, part_ml, slice_counters, err_flag};
+  switch (hd) {
+    case 64: return dec::launch<64>(mk, mv, a, n_entries, stream);
+    case 128: return dec::launch<128>(mk, mv, a, n_entries, stream);
+    case 192: return dec::launch<192>(mk, mv, a, n_entries, stream);
+    default: return dec::launch<256>(mk, mv, a, n_entries, stream);
+  }
+}

@@ -11,7 +11,8 @@
 //  * keys-split kernel (decode: at most 16 rows per entry and KV head): a block
 //    takes one entry, one KV head and one slice of the keys; its four warps
 //    share the 16 rows and each takes 16 keys of every tile; the warps' partial
-//    results are merged in shared memory, the slices' in a second kernel.
+//    results are merged in shared memory, and the slices' by whichever block of an
+//    (entry, KV head) finishes last.
 //
 // Softmax, its running maximum and sum, and the output accumulation are
 // float32.  Formula: src/model/math.rs:102-155.
@@ -42,6 +43,7 @@ struct AttnArgs {
   int nsplit;
   float* part_o;            // keys-split with nsplit > 1: [entry, kv head, slice, 16, hd]
   float* part_ml;           //                             [entry, kv head, slice, 16, 2]
+  int* slice_counters;      //                             [entry, kv head], zero on entry, left zero
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
@@ -77,22 +79,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Loads keys [jb, jb+KT) of one KV head into a tile [KT][stride] (bf16); keys outside
-// [first_key, n_keys) become zeros.
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* cache, const int* table, int jb,
-                                             int first_key, int n_keys, int kvh, const AttnArgs& a,
-                                             int stride) {
+// Loads keys [jb, jb+KT) of one KV head into a K tile and a V tile, each [KT][stride] (bf16); keys
+// outside [first_key, n_keys) become zeros.  One block-table lookup serves both tiles.
+__device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const int* table, int jb,
+                                              int first_key, int n_keys, int kvh, const AttnArgs& a,
+                                              int stride) {
   const int chunks = a.hd >> 3;                       // 16-byte chunks per row
-  for (int idx = threadIdx.x; idx < KT * chunks; idx += ATT_THREADS) {
-    const int key = idx / chunks, c = idx - key * chunks;
+  const bool pow2 = (a.page_size & (a.page_size - 1)) == 0;
+  const int shift = 31 - __clz(a.page_size);
+  auto one = [&](int key, int c) {
     const int j = jb + key;
     const bool valid = j >= first_key && j < n_keys;
-    const bf16* src = cache;
+    size_t off = 0;
     if (valid) {
-      const int page = table[j / a.page_size];
-      src = cache + (((size_t)page * a.page_size + j % a.page_size) * a.nkv + kvh) * a.hd + c * 8;
+      const int pg = pow2 ? (j >> shift) : (j / a.page_size);
+      const int in_page = j - pg * a.page_size;
+      off = (((size_t)table[pg] * a.nkv + kvh) * a.page_size + in_page) * a.hd + c * 8;
     }
-    cp_async_16(tile + key * stride + c * 8, src, valid);
+    cp_async_16(k_tile + key * stride + c * 8, a.k_cache + off, valid);
+    cp_async_16(v_tile + key * stride + c * 8, a.v_cache + off, valid);
+  };
+  if ((chunks & (chunks - 1)) == 0) {                 // head sizes 16, 32, 64, 128, 256: shifts only
+    const int cs = 31 - __clz(chunks);
+    const int c = threadIdx.x & (chunks - 1), k0 = threadIdx.x >> cs, kstep = ATT_THREADS >> cs;
+    for (int key = k0; key < KT; key += kstep) one(key, c);
+  } else {
+    for (int idx = threadIdx.x; idx < KT * chunks; idx += ATT_THREADS) one(idx / chunks, idx % chunks);
   }
 }
 
@@ -247,8 +259,7 @@ attention_rows_kernel(const AttnArgs a) {
   const int jb0 = (first_key / KT) * KT;
   const int n_tiles = (n_keys - jb0 + KT - 1) / KT;
 
-  load_kv_tile(kv_s, a.k_cache, table, jb0, first_key, n_keys, kvh, a, stride);
-  load_kv_tile(kv_s + tile_elems, a.v_cache, table, jb0, first_key, n_keys, kvh, a, stride);
+  load_kv_tiles(kv_s, kv_s + tile_elems, table, jb0, first_key, n_keys, kvh, a, stride);
   cp_async_commit();
 
   WarpTile<HD_MAX, 8> wt;
@@ -267,8 +278,7 @@ attention_rows_kernel(const AttnArgs a) {
     bf16* cur = kv_s + (t & 1) * 2 * tile_elems;
     if (t + 1 < n_tiles) {
       bf16* nxt = kv_s + ((t + 1) & 1) * 2 * tile_elems;
-      load_kv_tile(nxt, a.k_cache, table, jb + KT, first_key, n_keys, kvh, a, stride);
-      load_kv_tile(nxt + tile_elems, a.v_cache, table, jb + KT, first_key, n_keys, kvh, a, stride);
+      load_kv_tiles(nxt, nxt + tile_elems, table, jb + KT, first_key, n_keys, kvh, a, stride);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -305,13 +315,16 @@ attention_rows_kernel(const AttnArgs a) {
 // ---------------------------------------------------------------------------
 // keys-split kernel (at most 16 rows per entry and KV head)
 // ---------------------------------------------------------------------------
+constexpr int KEYS_STAGES = 3;
+
 template <int HD_MAX>
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_keys_kernel(const AttnArgs a) {
   extern __shared__ __align__(16) uint8_t att_smem[];
+  __shared__ int is_last;
   const int stride = a.hd + 8;
   bf16* q_s = reinterpret_cast<bf16*>(att_smem);            // [16][stride]
-  bf16* kv_s = q_s + 16 * stride;                           // [2 stages][K tile | V tile]
+  bf16* kv_s = q_s + 16 * stride;                           // [stages][K tile | V tile]
   const int tile_elems = KT * stride;
 
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
@@ -329,9 +342,8 @@ attention_keys_kernel(const AttnArgs a) {
     if (valid) src = a.q + ((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * a.hd + c * 8;
     cp_async_16(q_s + row * stride + c * 8, src, valid);
   }
-  const int n_keys_all = kv_len;                            // the last row sees every key
   const int first_key = a.window > 0 ? max(0, start - a.window + 1) : 0;
-  const int slice_lo = z * a.kv_chunk, slice_hi = min(n_keys_all, slice_lo + a.kv_chunk);
+  const int slice_lo = z * a.kv_chunk, slice_hi = min(kv_len, slice_lo + a.kv_chunk);
   const int jb0 = max(slice_lo, (first_key / KT) * KT);
   const int n_tiles = slice_hi > jb0 ? (slice_hi - jb0 + KT - 1) / KT : 0;
 
@@ -342,36 +354,35 @@ attention_keys_kernel(const AttnArgs a) {
   const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
   const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
 
-  if (n_tiles > 0) {
-    load_kv_tile(kv_s, a.k_cache, table, jb0, first_key, slice_hi, kvh, a, stride);
-    load_kv_tile(kv_s + tile_elems, a.v_cache, table, jb0, first_key, slice_hi, kvh, a, stride);
+  // prologue: the first STAGES-1 tiles are in flight before the loop (one commit group per tile)
+#pragma unroll
+  for (int p = 0; p < KEYS_STAGES - 1; ++p) {
+    if (p < n_tiles) {
+      bf16* dst = kv_s + p * 2 * tile_elems;
+      load_kv_tiles(dst, dst + tile_elems, table, jb0 + p * KT, first_key, slice_hi, kvh, a, stride);
+    }
+    cp_async_commit();
   }
-  cp_async_commit();
   for (int t = 0; t < n_tiles; ++t) {
     const int jb = jb0 + t * KT;
-    bf16* cur = kv_s + (t & 1) * 2 * tile_elems;
-    if (t + 1 < n_tiles) {
-      bf16* nxt = kv_s + ((t + 1) & 1) * 2 * tile_elems;
-      load_kv_tile(nxt, a.k_cache, table, jb + KT, first_key, slice_hi, kvh, a, stride);
-      load_kv_tile(nxt + tile_elems, a.v_cache, table, jb + KT, first_key, slice_hi, kvh, a, stride);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    bf16* cur = kv_s + (t % KEYS_STAGES) * 2 * tile_elems;
+    cp_async_wait<KEYS_STAGES - 2>();                       // tile t has landed
+    __syncthreads();                                        // ... and everyone is done with tile t-1
+    if (t + KEYS_STAGES - 1 < n_tiles) {
+      bf16* dst = kv_s + ((t + KEYS_STAGES - 1) % KEYS_STAGES) * 2 * tile_elems;
+      load_kv_tiles(dst, dst + tile_elems, table, jb + (KEYS_STAGES - 1) * KT, first_key, slice_hi, kvh, a,
+                    stride);
     }
-    __syncthreads();
+    cp_async_commit();
     if (t == 0) wt.load_q(q_s, stride, a.hd, 0);
     if (jb + warp * 16 < slice_hi) {
-      const bool need_mask = jb + KT > min(slice_hi, start + 1) || jb < first_key + 0 || a.window > 0;
+      const bool need_mask = jb + KT > min(slice_hi, start + 1) || a.window > 0;
       wt.step(cur, cur + tile_elems, stride, a.hd, warp * 16, jb, pos0, pos1, lo0, lo1, a.scale_log2,
               need_mask);
     }
-    __syncthreads();
   }
-  if (n_tiles == 0) {
-    cp_async_wait<0>();
-    __syncthreads();
-  }
+  cp_async_wait<0>();
+  __syncthreads();
   // merge the four warps: (m, l, O) of each warp -> shared memory (the tiles are no longer needed)
   float* ml_s = reinterpret_cast<float*>(kv_s);             // [4 warps][16 rows][2]
   float* o_s = ml_s + 4 * 16 * 2;                           // [4 warps][16 rows][hd]
@@ -392,6 +403,7 @@ attention_keys_kernel(const AttnArgs a) {
     }
   }
   __syncthreads();
+  const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
   for (int idx = threadIdx.x; idx < rows_total * a.hd; idx += ATT_THREADS) {
     const int row = idx / a.hd, d = idx - row * a.hd;
     float mm = -CUDART_INF_F;
@@ -409,33 +421,36 @@ attention_keys_kernel(const AttnArgs a) {
       a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * a.hd + d] =
           __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
     } else {
-      const size_t slab = ((size_t)e * a.nkv + kvh) * a.nsplit + z;
-      a.part_o[(slab * 16 + row) * a.hd + d] = oo;
+      a.part_o[((slab0 + z) * 16 + row) * a.hd + d] = oo;
       if (d == 0) {
-        a.part_ml[(slab * 16 + row) * 2 + 0] = mm;
-        a.part_ml[(slab * 16 + row) * 2 + 1] = ll;
+        a.part_ml[((slab0 + z) * 16 + row) * 2 + 0] = mm;
+        a.part_ml[((slab0 + z) * 16 + row) * 2 + 1] = ll;
       }
     }
   }
-}
-
-// Merges the slices of the keys-split kernel: one block per (entry, KV head).
-__global__ void attention_merge_kernel(const AttnArgs a) {
-  const int e = blockIdx.x, kvh = blockIdx.y;
-  const int g = a.nq / a.nkv;
-  const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0;
-  const int rows_total = q_len * g;
-  const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
-  for (int idx = threadIdx.x; idx < rows_total * a.hd; idx += blockDim.x) {
+  if (a.nsplit == 1) return;
+  // the last slice of this (entry, KV head) to finish merges all of them, in slice order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = a.slice_counters + e * a.nkv + kvh;
+    const int prev = atomicAdd(counter, 1);
+    is_last = prev == a.nsplit - 1;
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows_total * a.hd; idx += ATT_THREADS) {
     const int row = idx / a.hd, d = idx - row * a.hd;
     float mm = -CUDART_INF_F;
-    for (int z = 0; z < a.nsplit; ++z) mm = fmaxf(mm, a.part_ml[((slab0 + z) * 16 + row) * 2]);
+    for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]));
     const float base = mm == -CUDART_INF_F ? 0.f : mm;
     float ll = 0.f, oo = 0.f;
-    for (int z = 0; z < a.nsplit; ++z) {
-      const float f = exp2f(a.part_ml[((slab0 + z) * 16 + row) * 2] - base);
-      ll += a.part_ml[((slab0 + z) * 16 + row) * 2 + 1] * f;
-      oo += a.part_o[((slab0 + z) * 16 + row) * a.hd + d] * f;
+    for (int s = 0; s < a.nsplit; ++s) {
+      const float f = exp2f(__ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]) - base);
+      ll += __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2 + 1]) * f;
+      oo += __ldcg(&a.part_o[((slab0 + s) * 16 + row) * a.hd + d]) * f;
     }
     a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * a.hd + d] =
         __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
@@ -459,19 +474,14 @@ static int launch_rows(const AttnArgs& a, int n_work, cudaStream_t stream) {
 template <int HD_MAX>
 static int launch_keys(const AttnArgs& a, int n_entries, cudaStream_t stream) {
   const int stride = a.hd + 8;
-  size_t smem = (size_t)(16 + 4 * KT) * stride * 2;
-  const size_t merge = (size_t)16 * stride * 2 + (size_t)(4 * 16 * 2 + 4 * 16 * a.hd) * 4;
-  if (merge > smem) smem = merge;
+  const size_t smem = (size_t)(16 + 2 * KEYS_STAGES * KT) * stride * 2;   // the merge area fits in the tiles
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(attention_keys_kernel<HD_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (16 + 4 * KT) * (HD_MAX + 8) * 2 + 4 * 16 * 2 * 4 + 4096);
+                         (16 + 2 * KEYS_STAGES * KT) * (HD_MAX + 8) * 2);
     configured = true;
   }
   attention_keys_kernel<HD_MAX><<<dim3(n_entries, a.nkv, a.nsplit), ATT_THREADS, smem, stream>>>(a);
-  int st = launched();
-  if (st != ST_OK || a.nsplit == 1) return st;
-  attention_merge_kernel<<<dim3(n_entries, a.nkv), 128, 0, stream>>>(a);
   return launched();
 }
 
@@ -497,7 +507,7 @@ extern "C" int srlm_paged_attention_rows(const void* q, const void* k_cache, con
   if (st != ST_OK) return st;
   AttnArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, table_stride,
              cu_q, kv_lens, work, nq, nkv, hd, page_size, scale * 1.4426950408889634f, window, 0, 1, nullptr,
-             nullptr};
+             nullptr, nullptr};
   if (hd <= 64) return launch_rows<64>(a, n_work, stream);
   if (hd <= 128) return launch_rows<128>(a, n_work, stream);
   return launch_rows<256>(a, n_work, stream);
@@ -505,21 +515,21 @@ extern "C" int srlm_paged_attention_rows(const void* q, const void* k_cache, con
 
 // Every entry has at most 16 rows (q tokens * nq/nkv).  nsplit slices of kv_chunk keys (a multiple of 64)
 // must cover the longest entry.  With nsplit > 1: part_o holds n_entries*nkv*nsplit*16*hd floats, part_ml
-// n_entries*nkv*nsplit*32 floats.
+// n_entries*nkv*nsplit*32 floats, slice_counters n_entries*nkv ints that are zero on entry (and on exit).
 extern "C" int srlm_paged_attention_keys(const void* q, const void* k_cache, const void* v_cache, void* out,
                                          const int* block_table, int table_stride, const int* cu_q,
                                          const int* kv_lens, int n_entries, int nq, int nkv, int hd, int page_size,
                                          float scale, int window, int kv_chunk, int nsplit, float* part_o,
-                                         float* part_ml, cudaStream_t stream) {
+                                         float* part_ml, int* slice_counters, cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
   int st = check_common("paged_attention_keys", nq, nkv, hd, page_size);
   if (st != ST_OK) return st;
-  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % KT || (nsplit > 1 && (!part_o || !part_ml)))
+  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % KT || (nsplit > 1 && (!part_o || !part_ml || !slice_counters)))
     return refuse(ST_BAD_SIZE, "paged_attention_keys: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
   if (nsplit > 65535 || nkv > 65535) return refuse(ST_BAD_SIZE, "paged_attention_keys: grid too large");
   AttnArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, table_stride,
              cu_q, kv_lens, nullptr, nq, nkv, hd, page_size, scale * 1.4426950408889634f, window, kv_chunk, nsplit,
-             part_o, part_ml};
+             part_o, part_ml, slice_counters};
   if (hd <= 64) return launch_keys<64>(a, n_entries, stream);
   if (hd <= 128) return launch_keys<128>(a, n_entries, stream);
   return launch_keys<256>(a, n_entries, stream);

@@ -48,7 +48,7 @@ __global__ void paged_attention_simt_kernel(
     size_t row = 0;
     if (valid) {
       const int page = table[j / page_size];
-      row = ((size_t)page * page_size + (j % page_size)) * nkv + kvh;
+      row = ((size_t)page * nkv + kvh) * page_size + (j % page_size);
       const TC* kp = k_cache + row * hd;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot += qv[d] * to_float(kp[d]);

@@ -157,7 +157,7 @@ template <int BN>
 constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -271,15 +271,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*last_flag && n < args.N) {
         __threadfence();
-        for (int j = 0; j < BN; ++j) {
-          const int m = m0 + j;
-          if (m >= args.M) break;
-          float x = 0.f;
-          for (int z = 0; z < (int)gridDim.z; ++z)
-            x += __ldcg(&args.partial[((size_t)z * args.M + m) * args.N + n]);
-          const size_t at = (size_t)m * args.ldc + n;
-          if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x;
-          else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x);
+        const int rows = min(BN, args.M - m0), nz = (int)gridDim.z;
+        const size_t slab = (size_t)args.M * args.N;
+        for (int j = 0; j < rows; j += 4) {
+          // four rows at a time: the loads of a row do not wait for the sums of the one before
+          float x[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int z = 0; z < nz; ++z) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (j + u < rows) x[u] += __ldcg(&args.partial[z * slab + (size_t)(m0 + j + u) * args.N + n]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (j + u < rows) {
+              const size_t at = (size_t)(m0 + j + u) * args.ldc + n;
+              if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x[u];
+              else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x[u]);
+            }
+          }
         }
       }
     }
@@ -404,10 +413,13 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   const CUtensorMap* mx = cached_map(X, M, K, ldx, bn, false);
   if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
   switch (bn) {
-    case 16: return launch<16, 10>(mw, mx, a, splits, stream);
-    case 32: return launch<32, 8>(mw, mx, a, splits, stream);
-    case 64: return launch<64, 8>(mw, mx, a, splits, stream);
-    case 128: return launch<128, 6>(mw, mx, a, splits, stream);
+    // few stages per block so that three (two at 128 tokens) blocks share an SM: their prologues and
+    // epilogues overlap one another's streaming, and tile counts that are no multiple of 148 still
+    // keep every SM busy; the bytes in flight per SM stay the same
+    case 16: return launch<16, 4>(mw, mx, a, splits, stream);
+    case 32: return launch<32, 3>(mw, mx, a, splits, stream);
+    case 64: return launch<64, 3>(mw, mx, a, splits, stream);
+    case 128: return launch<128, 3>(mw, mx, a, splits, stream);
     default: return launch<256, 4>(mw, mx, a, splits, stream);
   }
 }

@@ -26,13 +26,14 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, float* __re
 // One warp per (token, head) of the fused projection output
 // qkv[T, (nq + 2 nkv) * hd]: heads [0,nq) are queries, [nq, nq+nkv) keys, then values.
 // kv_slot[t] = page * page_size + offset of token t in this cache group, or -1 to skip the append.
+// Cache layout: [page, kv head, token in page, head_dim], so a KV head's share of a page is contiguous.
 template <typename TA, typename TC>
 __global__ void qk_norm_rope_append_kernel(
     const TA* __restrict__ qkv, TA* __restrict__ q_out, TC* __restrict__ k_cache,
     TC* __restrict__ v_cache, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
     float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     const int* __restrict__ kv_slot, int T, int nq, int nkv, int hd, int rotary_half,
-    int heads_total, int write_kv) {
+    int heads_total, int write_kv, int page_size) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= T * heads_total) return;
@@ -45,7 +46,7 @@ __global__ void qk_norm_rope_append_kernel(
   if (!is_q && slot < 0) return;
 
   if (!is_q && !is_k) {   // value: copy
-    TC* dst = v_cache + ((size_t)slot * nkv + (head - nq - nkv)) * hd;
+    TC* dst = v_cache + (((size_t)(slot / page_size) * nkv + (head - nq - nkv)) * page_size + slot % page_size) * hd;
     for (int d = lane; d < hd; d += 32) dst[d] = from_float<TC>(to_float(src[d]));
     return;
   }
@@ -58,7 +59,8 @@ __global__ void qk_norm_rope_append_kernel(
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
   TA* qdst = is_q ? q_out + ((size_t)t * nq + head) * hd : nullptr;
-  TC* kdst = is_k ? k_cache + ((size_t)slot * nkv + (head - nq)) * hd : nullptr;
+  TC* kdst = is_k ? k_cache + (((size_t)(slot / page_size) * nkv + (head - nq)) * page_size + slot % page_size) * hd
+                  : nullptr;
   auto put = [&](int d, float v) {
     if (is_q) qdst[d] = from_float<TA>(v); else kdst[d] = from_float<TC>(v);
   };
@@ -96,10 +98,10 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
                                         void* v_cache, int cache_dtype, const float* q_norm_w,
                                         const float* k_norm_w, float eps, const float* cos_t,
                                         const float* sin_t, const int* kv_slot, int T, int nq,
-                                        int nkv, int hd, int rotary_half, int write_kv,
+                                        int nkv, int hd, int rotary_half, int write_kv, int page_size,
                                         cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  if (nq <= 0 || nkv <= 0 || hd <= 0 || rotary_half < 0 || 2 * rotary_half > hd)
+  if (nq <= 0 || nkv <= 0 || hd <= 0 || rotary_half < 0 || 2 * rotary_half > hd || page_size <= 0)
     return refuse(ST_BAD_SIZE, "qk_norm_rope_append: nq=%d nkv=%d hd=%d rotary_half=%d", nq, nkv, hd,
                   rotary_half);
   if (act_dtype != cache_dtype)
@@ -111,6 +113,6 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
   const long long grid = (warps * 32 + block - 1) / block;
   SRLM_DISPATCH_ACT(act_dtype, TA, (qk_norm_rope_append_kernel<TA, TA><<<(unsigned)grid, block, 0, stream>>>(
       (const TA*)qkv, (TA*)q_out, (TA*)k_cache, (TA*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t,
-      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv)));
+      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv, page_size)));
   return launched();
 }

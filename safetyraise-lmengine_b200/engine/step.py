@@ -54,6 +54,13 @@ class Engine:
         self._meta_hosts: list = []          # ring of pinned buffers, each with the event of its last copy
         self._meta_turn = 0
         self.steps_run = 0
+        # decode-only steps (one token per entry) are recorded into CUDA graphs, one per
+        # (batch size, wanted rows, block-table width); the second step of a kind records, later ones replay
+        self.use_graphs = bool(mctx.options.get("cuda_graphs", True))
+        self._graphs: Dict[tuple, tuple] = {}
+        self._graph_seen: set = set()
+        self.graph_replays = 0
+        self._graph_generation = 0
         self.last_h2d_bytes = 0          # bytes of batch layout the last step copied to the device
 
     # ---- construction -----------------------------------------------------
@@ -129,6 +136,7 @@ class Engine:
         if self._meta_dev is None or self._meta_dev.numel() < words:
             cap = max(words, 4 * self.mctx.max_batch_tokens + 64 * (self.max_pages_per_request + 8) + 1024)
             torch.cuda.synchronize(self.mctx.device)
+            self._graphs.clear()                      # they point into the old buffer
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.mctx.device)
             self._meta_hosts = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), None]
                                 for _ in range(4)]
@@ -146,7 +154,9 @@ class Engine:
         groups = self.cache.paged_groups
         ps = self.cache.page_size
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
-        pages = _round_up(max(1, max((l + ps - 1) // ps for l in kv_lens)), 8)
+        # decode-only steps round the table width coarsely: its value is part of a graph's identity
+        decode_only = max(q_lens) == 1
+        pages = _round_up(max(1, max((l + ps - 1) // ps for l in kv_lens)), 16 if decode_only else 8)
         R = sum(len(e.want) for e in entries)
         # layout, in int32 words; every section starts on a 16-byte boundary
         sections, off = {}, 0
@@ -208,6 +218,35 @@ class Engine:
             cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
             max_q_len=max(q_lens), max_kv_len=max(kv_lens), kv_bound=pages * ps)
 
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        """Runs the model on the batch: eagerly, or by replaying the CUDA graph of this kind of step."""
+        from ..kernels import ops
+        if not self.use_graphs or ctx.max_q_len != 1:
+            return self.model.forward(ctx)
+        if self._graph_generation != self.workspace.generation:   # a buffer moved since recording
+            self._graphs.clear()
+            self._graph_generation = self.workspace.generation
+        key = (ctx.T, ctx.n_entries, int(ctx.logit_rows.shape[0]), ctx.kv_bound)
+        hit = self._graphs.get(key)
+        if hit is None:
+            if key not in self._graph_seen:           # first time: run eagerly (this also sizes every buffer)
+                self._graph_seen.add(key)
+                return self.model.forward(ctx)
+            if len(self._graphs) >= 64:
+                self._graphs.clear()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            torch.cuda.synchronize(self.mctx.device)
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            hit = self._graphs[key] = (graph, logits, ops.launches - before)
+            ops.launches = before
+        graph, logits, launches = hit
+        graph.replay()
+        ops.launches += launches
+        self.graph_replays += 1
+        return logits
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""
         self._validate(entries)
@@ -223,7 +262,7 @@ class Engine:
         try:
             with torch.cuda.device(self.mctx.device):
                 ctx = self.build_context(entries, starts)
-                logits = self.model.forward(ctx)
+                logits = self._forward(ctx)
         except Exception:
             for e, s in done:
                 self.cache.truncate(e.slot, s)

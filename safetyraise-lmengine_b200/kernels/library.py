@@ -45,6 +45,7 @@ class KernelLibrary:
         self.launches = 0          # kernels launched through this object (a benchmark reports it)
         self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
         self.force_simt_attention = False
+        self.force_cp_async_decode = False
 
     @property
     def lib(self):
@@ -101,12 +102,13 @@ class KernelLibrary:
 
     def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos, sin, kv_slot,
                             nq, nkv, hd, rotary_half, write_kv=True):
+        """k_cache / v_cache: [pages, kv_heads, page_size, head_dim]; kv_slot[t] = page * page_size + offset."""
         T = qkv.shape[0]
         self._check(self.lib.srlm_qk_norm_rope_append(
             _ptr(qkv), _ptr(q_out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
             dtype_code(k_cache.dtype), _ptr(q_norm_w), _ptr(k_norm_w), C.c_float(eps), _ptr(cos), _ptr(sin),
             _ptr(kv_slot), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(rotary_half),
-            C.c_int(int(write_kv)), _stream()), "qk_norm_rope_append")
+            C.c_int(int(write_kv)), C.c_int(k_cache.shape[2]), _stream()), "qk_norm_rope_append")
 
     # ---- attention --------------------------------------------------------
     def paged_attention_simt(self, q, k_cache, v_cache, out, block_table, entry_of_token, positions,
@@ -151,16 +153,23 @@ class KernelLibrary:
 
     @staticmethod
     def gemm_splits(M: int, N: int, K: int) -> int:
-        """How many ways to split K so that a skinny product still fills the 148 SMs."""
+        """How many ways to split K: the number of blocks should fill whole waves of the 148 SMs
+        (192 tiles alone would leave the second wave two thirds empty), each split keeping at
+        least 4 k-blocks, the partial sums fitting the workspace."""
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
         total_kb = (K + 63) // 64
-        if tiles >= 120:
+        if tiles >= 1024 or M > 256:
             return 1
-        splits = max(1, min(148 // tiles, total_kb // 4, 16))
-        while splits > 1 and 65536 + splits * M * N * 4 > KernelLibrary.GEMM_WS_BYTES:
-            splits -= 1
-        return splits
+        best, best_eff = 1, 0.0
+        for s in range(1, 17):
+            if s > 1 and (total_kb // s < 4 or 65536 + s * M * N * 4 > KernelLibrary.GEMM_WS_BYTES):
+                break
+            blocks = tiles * s
+            eff = blocks / (-(-blocks // 148) * 148)
+            if eff > best_eff + 0.04:
+                best, best_eff = s, eff
+        return best
 
     def gemm_tn_tcgen05(self, a, w, out, splits=None):
         """out[M,N] = a[M,K] @ w[N,K]^T, bfloat16 operands, tcgen05 tensor cores, float32 accumulation."""
@@ -198,11 +207,39 @@ class KernelLibrary:
     def paged_attention_keys(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv, hd,
                              page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
         """bfloat16 tensor-core attention when every entry has at most 16 rows (decode); keys in nsplit slices."""
+        counters = None
+        if nsplit > 1:
+            counters = getattr(self, "_slice_counters", None)
+            if counters is None or counters.device != q.device:
+                counters = self._slice_counters = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)
+            if n_entries * nkv > counters.numel():
+                raise ShapeError(f"paged_attention_keys: {n_entries} entries x {nkv} KV heads exceed the counters")
         self._check(self.lib.srlm_paged_attention_keys(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), C.c_int(block_table.stride(0)),
             _ptr(cu_q), _ptr(kv_lens), C.c_int(n_entries), C.c_int(nq), C.c_int(nkv), C.c_int(hd),
             C.c_int(page_size), C.c_float(scale), C.c_int(window or 0), C.c_int(kv_chunk), C.c_int(nsplit),
-            _ptr(part_o), _ptr(part_ml), _stream()), "paged_attention_keys")
+            _ptr(part_o), _ptr(part_ml), _ptr(counters), _stream()), "paged_attention_keys")
+
+    def _slice_counter_buffer(self, device, need):
+        counters = getattr(self, "_slice_counters", None)
+        if counters is None or counters.device != device:
+            counters = self._slice_counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        if need > counters.numel():
+            raise ShapeError(f"attention: {need} (entry, KV head) pairs exceed the slice counters")
+        return counters
+
+    def paged_attention_decode_tma(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv,
+                                   hd, page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
+        """Decode attention with TMA page loads (head_dim a multiple of 64; page_size 8, 16, 32 or a
+        multiple of 64); same contract as paged_attention_keys."""
+        counters = self._slice_counter_buffer(q.device, n_entries * nkv) if nsplit > 1 else None
+        err = self._gemm_state(q.device)[1]
+        self._check(self.lib.srlm_paged_attention_decode_tma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+            C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), C.c_int(n_entries), C.c_int(nq),
+            C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+            C.c_int(kv_chunk), C.c_int(nsplit), _ptr(part_o), _ptr(part_ml), _ptr(counters), _ptr(err),
+            _stream()), "paged_attention_decode_tma")
 
     @staticmethod
     def attention_split(n_entries: int, nkv: int, max_kv: int):
@@ -225,6 +262,17 @@ class KernelLibrary:
         g = nq // nkv
         if ctx.max_q_len * g <= 16:
             nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
+            if self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size)) and not self.force_cp_async_decode:
+                part_o = part_ml = None
+                if nsplit > 1:
+                    part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,
+                                               reserve=0)
+                    part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2,
+                                                torch.float32, reserve=0)
+                self.paged_attention_decode_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
+                                                ctx.n_entries, nq, nkv, hd, page_size, scale, window, chunk,
+                                                nsplit, part_o, part_ml)
+                return
             part_o = part_ml = None
             if nsplit > 1:
                 part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,

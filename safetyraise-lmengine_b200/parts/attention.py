@@ -74,5 +74,5 @@ class PagedAttention(Part):
                                 write_kv=run_step.writes_cache)
         attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
         ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
-                            s.head_dim, k_pool.shape[1], s.softmax_scale, s.window or 0)
+                            s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0)
         return self.out(ctx, attended, "attn.proj")

@@ -79,6 +79,7 @@ class Workspace:
     def __init__(self, device, max_tokens: int):
         self.device, self.max_tokens = device, max_tokens
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self.generation = 0      # grows whenever a buffer moves: recorded CUDA graphs are stale then
 
     def get(self, name: str, rows: int, width: int, dtype: torch.dtype, reserve=None) -> torch.Tensor:
         """A [rows, width] view of the buffer ``name``; the buffer is made for ``reserve`` rows
@@ -87,6 +88,8 @@ class Workspace:
         buf = self._bufs.get(key)
         cap = max(rows, self.max_tokens if reserve is None else reserve, 1)
         if buf is None or buf.shape[0] < rows:
+            if buf is not None:
+                self.generation += 1
             buf = torch.empty((cap, width), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:rows]

@@ -151,3 +151,27 @@ def test_refused_step_changes_nothing(folder_a):
     s2 = eng.open_request()
     again = eng.step([StepEntry(s2, [1, 2, 3, 4, 5], [4])]).cpu().numpy()
     assert np.array_equal(ref, again)
+
+
+def test_recorded_decode_steps_equal_eager_ones(folder_b):
+    """Decode-only steps replay a CUDA graph from their third occurrence on: same logits as eager."""
+    cfg, _ = TINY["B"]
+    rng = np.random.default_rng(9)
+    prompts = {r: random_tokens(rng, n, cfg["vocab_size"]) for r, n in (("p", 20), ("q", 33))}
+    tails = {r: random_tokens(rng, 40, cfg["vocab_size"]) for r in prompts}
+    results = []
+    for graphs in (False, True):
+        eng = build(folder_b, "bfloat16", options={"cuda_graphs": graphs})
+        steps = [{"entries": [(r, prompts[r], []) for r in prompts]}]
+        steps += [{"entries": [(r, [tails[r][i]], [0]) for r in prompts]} for i in range(40)]
+        results.append(replay(eng, steps))
+        assert (eng.graph_replays > 30) == graphs
+    eager, recorded = results
+    assert eager.keys() == recorded.keys()
+    for k in eager:
+        assert np.array_equal(eager[k], recorded[k]), k
+    both = {r: prompts[r] + tails[r] for r in prompts}
+    for r, toks in both.items():
+        ref = plain_logits(folder_b, toks)
+        for p in range(len(prompts[r]), len(toks)):
+            assert np.abs(recorded[(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()

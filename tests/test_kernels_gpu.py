@@ -119,8 +119,8 @@ def test_qk_norm_rope_append(nq, nkv, hd, rd, dt, with_norm):
     ops().rope_table(pos, cos, sin, 1e4, rd)
     slots = torch.randperm(pages * ps, device=DEV, generator=g)[:T].to(torch.int32)
     slots[5] = -1                                   # this token's keys are not kept
-    kc = torch.full((pages, ps, nkv, hd), 7.0, device=DEV, dtype=dt)
-    vc = torch.full((pages, ps, nkv, hd), 7.0, device=DEV, dtype=dt)
+    kc = torch.full((pages, nkv, ps, hd), 7.0, device=DEV, dtype=dt)     # [page, kv head, token, dim]
+    vc = torch.full((pages, nkv, ps, hd), 7.0, device=DEV, dtype=dt)
     q = torch.empty(T, nq * hd, device=DEV, dtype=dt)
     ops().qk_norm_rope_append(qkv, q, kc, vc, qw, kw, eps, cos, sin, slots, nq, nkv, hd, half)
     x = qkv.float().view(T, nq + 2 * nkv, hd)
@@ -128,7 +128,8 @@ def test_qk_norm_rope_append(nq, nkv, hd, rd, dt, with_norm):
     k_ref = ref_norm_rope(x[:, nq:nq + nkv], kw, eps, cos, sin, half)
     v_ref = x[:, nq + nkv:]
     assert torch.allclose(q.float().view(T, nq, hd), q_ref, **tol(dt))
-    kflat, vflat = kc.float().view(pages * ps, nkv, hd), vc.float().view(pages * ps, nkv, hd)
+    kflat = kc.float().permute(0, 2, 1, 3).reshape(pages * ps, nkv, hd)
+    vflat = vc.float().permute(0, 2, 1, 3).reshape(pages * ps, nkv, hd)
     for t in range(T):
         if slots[t] < 0:
             continue
@@ -152,7 +153,8 @@ def ref_paged_attention(q, kc, vc, tables, entry_of_token, positions, nq, nkv, h
         lo = max(0, p - window + 1) if window else 0
         js = torch.arange(lo, p + 1)
         rows = torch.tensor([tables[e][j // ps] for j in js.tolist()]) * ps + js % ps
-        kf, vf = kd.view(-1, nkv, hd)[rows], vd.view(-1, nkv, hd)[rows]
+        kf = kd.permute(0, 2, 1, 3).reshape(-1, nkv, hd)[rows]      # caches are [page, kv head, token, dim]
+        vf = vd.permute(0, 2, 1, 3).reshape(-1, nkv, hd)[rows]
         for h in range(nq):
             kh = h // (nq // nkv)
             s = (kf[:, kh] @ qd[t, h]) * scale
@@ -165,8 +167,8 @@ def make_paged_case(nq, nkv, hd, ps, dt, lens_q, lens_kv, seed=5, pages=64):
     g = torch.Generator(device=DEV).manual_seed(seed)
     n = len(lens_q)
     T = sum(lens_q)
-    kc = torch.randn(pages, ps, nkv, hd, device=DEV, generator=g).to(dt)
-    vc = torch.randn(pages, ps, nkv, hd, device=DEV, generator=g).to(dt)
+    kc = torch.randn(pages, nkv, ps, hd, device=DEV, generator=g).to(dt)
+    vc = torch.randn(pages, nkv, ps, hd, device=DEV, generator=g).to(dt)
     q = torch.randn(T, nq * hd, device=DEV, generator=g).to(dt)
     perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
     tables, used = [], 0
@@ -210,11 +212,11 @@ def test_paged_attention_finds_one_far_key():
     for far in (0, 15, 16, 333, 699):
         kc2 = kc * 0.01
         page, off = tables[0][far // ps], far % ps
-        kc2[page, off] = q.view(nq, hd)[0::2] * 4.0        # heads 0 and 2 -> kv heads 0 and 1
+        kc2[page, :, off] = q.view(nq, hd)[0::2] * 4.0     # heads 0 and 2 -> kv heads 0 and 1
         ops().paged_attention_simt(q, kc2, vc, out, bt, eot, pos, nq, nkv, hd, ps, 1.0, 0)
         got = out.view(nq, hd)
         for h, kh in ((0, 0), (2, 1)):
-            assert torch.allclose(got[h], vc[page, off, kh], atol=1e-3), (far, h)
+            assert torch.allclose(got[h], vc[page, kh, off], atol=1e-3), (far, h)
 
 
 @pytest.mark.parametrize("M, N, K", [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 129, 33), (17, 384, 96),
@@ -366,7 +368,7 @@ def test_mma_attention_finds_one_far_key(kernel):
         q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, [1], [700], pages=48)
         kc = kc * 0.01
         page, off = tables[0][far // ps], far % ps
-        kc[page, off] = q.view(nq, hd)[0::4] * 4.0                 # heads 0 and 4 -> kv heads 0 and 1
+        kc[page, :, off] = q.view(nq, hd)[0::4] * 4.0              # heads 0 and 4 -> kv heads 0 and 1
         out = torch.empty_like(q)
         cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
         kvl = torch.tensor([700], dtype=torch.int32, device=DEV)
@@ -379,4 +381,44 @@ def test_mma_attention_finds_one_far_key(kernel):
             ops().paged_attention_keys(q, kc, vc, out, bt, cu, kvl, 1, nq, nkv, hd, ps, 1.0, 0, 192, 4, part_o, part_ml)
         got = out.float().view(nq, hd)
         for h, kh in ((0, 0), (4, 1)):
-            assert torch.allclose(got[h], vc[page, off, kh].float(), atol=2e-2), (far, h)
+            assert torch.allclose(got[h], vc[page, kh, off].float(), atol=2e-2), (far, h)
+
+
+@pytest.mark.parametrize("nq, nkv, hd, ps", [(32, 8, 128, 16), (8, 2, 64, 16), (4, 4, 64, 8), (16, 1, 128, 32),
+                                             (6, 2, 192, 64), (2, 1, 256, 128)])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("nsplit", [1, 3])
+def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
+    g = nq // nkv
+    ql = max(1, min(3, 16 // g))
+    lens_q, lens_kv = [1, ql, 1, 1, ql], [1, 40, 65, 300, 129]
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=160)
+    used = torch.zeros(160, dtype=torch.bool)
+    for t in tables:
+        used[t] = True
+    kc[~used.to(DEV)] = float("nan")                  # pages of nobody: reading them must not matter
+    vc[~used.to(DEV)] = float("nan")
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    n = len(lens_q)
+    chunk = ((max(lens_kv) + nsplit - 1) // nsplit + 63) // 64 * 64
+    part_o = torch.full((n * nkv * nsplit * 16, hd), float("nan"), device=DEV)
+    part_ml = torch.full((n * nkv * nsplit * 16, 2), float("nan"), device=DEV)
+    out = torch.full_like(q, float("nan"))
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_decode_tma(q, kc, vc, out, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
+                                     part_o, part_ml)
+    assert ops().gemm_error_flag(q.device) == 0
+    kc[~used.to(DEV)] = 0
+    vc[~used.to(DEV)] = 0
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
+    # the tail of each request's last page is poisoned too: rows nobody wrote
+    for t, kv in zip(tables, lens_kv):
+        if kv % ps:
+            vc[t[-1], :, kv % ps:] = float("nan")
+            kc[t[-1], :, kv % ps:] = float("nan")
+    out2 = torch.full_like(q, float("nan"))
+    ops().paged_attention_decode_tma(q, kc, vc, out2, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
+                                     part_o, part_ml)
+    assert torch.equal(out, out2)
