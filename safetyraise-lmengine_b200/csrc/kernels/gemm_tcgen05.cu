@@ -423,3 +423,92 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     default: return launch<256, 4>(mw, mx, a, splits, stream);
   }
 }
+
+// ---------------------------------------------------------------------------
+// The same product for callers that cannot allocate device memory: the split-K
+// scratch is a device array inside the library image.  See srlm_no_alloc.h.
+// ---------------------------------------------------------------------------
+#include "srlm_no_alloc.h"
+
+namespace srlm {
+// [0, 65536): tile counters (zero on entry to the kernel); from 65536 on: float32 partial sums.
+static __device__ __align__(256) unsigned char g_static_scratch[SRLM_STATIC_SCRATCH_BYTES];
+static __device__ int g_static_err_flag;
+
+constexpr int kMaxDevices = 64;
+// Device addresses of the two symbols, looked up once per device.  In host code the symbols' names
+// are only handles for cudaGetSymbolAddress; a kernel must be given the looked-up pointers.
+static void* g_scratch_ptr[kMaxDevices];
+static int* g_err_ptr[kMaxDevices];
+static std::mutex g_static_mutex;
+
+static int static_setup(int device) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_scratch_ptr[device]) return ST_OK;
+  void* scratch = nullptr;
+  void* flag = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&scratch, g_static_scratch);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_static: cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+  e = cudaGetSymbolAddress(&flag, g_static_err_flag);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_static: cudaGetSymbolAddress(flag): %s", cudaGetErrorString(e));
+  g_err_ptr[device] = static_cast<int*>(flag);
+  g_scratch_ptr[device] = scratch;
+  return ST_OK;
+}
+}  // namespace srlm
+
+extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                           long long ldx, long long ldw, long long ldc, int splits,
+                                           int* err_flag_out, cudaStream_t stream) {
+  if (M <= 0) return ST_OK;
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < N)
+    return refuse(ST_BAD_SIZE, "gemm_static: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
+  if (K % 8 || ldx % 8 || ldw % 8)
+    return refuse(ST_BAD_SIZE, "gemm_static: K=%d and the leading dimensions must be multiples of 8", K);
+  if (((uintptr_t)X | (uintptr_t)W) & 15) return refuse(ST_BAD_ALIGN, "gemm_static: operands must be 16-byte aligned");
+  if (c_dtype != DT_F32 && c_dtype != DT_BF16) return refuse(ST_BAD_DTYPE, "gemm_static: output dtype %d", c_dtype);
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > total_kb) splits = total_kb;
+  const int kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kb_per_split - 1) / kb_per_split;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
+  const long long need = 65536 + (long long)splits * M * N * 4;
+  if (splits > 1 && (need > SRLM_STATIC_SCRATCH_BYTES || tiles * 4 > 65536))
+    return refuse(ST_BAD_SIZE, "gemm_static: %d splits of a %d x %d product need %lld bytes of scratch, the "
+                  "built-in array holds %d; use fewer splits or the entry point that takes a workspace",
+                  splits, M, N, need, (int)SRLM_STATIC_SCRATCH_BYTES);
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return refuse(ST_BAD_SIZE, "gemm_static: no usable current device (%s)", cudaGetErrorString(e));
+  int st = static_setup(device);
+  if (st != ST_OK) return st;
+  unsigned char* scratch = static_cast<unsigned char*>(g_scratch_ptr[device]);
+  int* err = g_err_ptr[device];
+  // what has to start at zero: the error flag always, the tile counters when they are used
+  e = cudaMemsetAsync(err, 0, sizeof(int), stream);
+  if (e == cudaSuccess && splits > 1) e = cudaMemsetAsync(scratch, 0, (size_t)tiles * 4, stream);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_static: clearing the scratch: %s", cudaGetErrorString(e));
+  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err, kb_per_split, nullptr, nullptr};
+  if (splits > 1) {
+    a.tile_counters = reinterpret_cast<int*>(scratch);
+    a.partial = reinterpret_cast<float*>(scratch + 65536);
+  }
+  CUtensorMap mw, mx;       // built on the stack: nothing is cached, nothing is allocated
+  if (!make_map(&mw, W, N, K, ldw, BM, true) || !make_map(&mx, X, M, K, ldx, bn, false))
+    return refuse(ST_BAD_SIZE, "gemm_static: cuTensorMapEncodeTiled refused the operands");
+  switch (bn) {
+    case 16: st = launch<16, 4>(&mw, &mx, a, splits, stream); break;
+    case 32: st = launch<32, 3>(&mw, &mx, a, splits, stream); break;
+    case 64: st = launch<64, 3>(&mw, &mx, a, splits, stream); break;
+    case 128: st = launch<128, 3>(&mw, &mx, a, splits, stream); break;
+    default: st = launch<256, 4>(&mw, &mx, a, splits, stream); break;
+  }
+  if (st != ST_OK || !err_flag_out) return st;
+  e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess) e = cudaMemcpy(err_flag_out, err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_static: reading the error flag: %s", cudaGetErrorString(e));
+  return ST_OK;
+}
