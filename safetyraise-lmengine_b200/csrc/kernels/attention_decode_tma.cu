@@ -90,6 +90,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -132,6 +140,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* empty_bar = full_bar + STAGES;
   __shared__ int is_last;
 
+  pdl_trigger();
+  if (threadIdx.x == 0) {                 // nothing here depends on the kernel ahead
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CONSUMERS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  pdl_wait();
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -144,10 +160,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int jb0 = max(slice_lo, (first_key / KT) * KT);
   const int n_tiles = slice_hi > jb0 ? (slice_hi - jb0 + KT - 1) / KT : 0;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CONSUMERS); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
   // Q rows -> shared memory (plain loads: 16 rows at most)
   for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
     const int row = idx / (HD / 8), c = idx % (HD / 8);
@@ -169,6 +181,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int ps = a.page_size;
       const int box_rows = ps < KT ? ps : KT;          // keys per TMA copy
       const int boxes = KT / box_rows;
+      uint64_t stream_once;                            // the cache is read once per step: first to leave L2
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_once));
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % STAGES, j = t / STAGES;
         if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, a.err_flag, 11)) break;
@@ -184,8 +198,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           const int row = (page * a.nkv + kvh) * ps + key % ps;      // row of the [pages*nkv*ps, HD] view
 #pragma unroll
           for (int p = 0; p < PANELS; ++p) {
-            tma_load_2d(kt + p * (KT * 128) + b * box_rows * 128, &map_k, &full_bar[s], p * 64, row);
-            tma_load_2d(vt + p * (KT * 128) + b * box_rows * 128, &map_v, &full_bar[s], p * 64, row);
+            tma_load_2d_hint(kt + p * (KT * 128) + b * box_rows * 128, &map_k, &full_bar[s], p * 64, row, stream_once);
+            tma_load_2d_hint(vt + p * (KT * 128) + b * box_rows * 128, &map_v, &full_bar[s], p * 64, row, stream_once);
           }
         }
       }
@@ -416,7 +430,8 @@ static int launch(const CUtensorMap* mk, const CUtensorMap* mv, const Args& a, i
     if (err != cudaSuccess) return refuse((int)err, "attention_decode_tma: cannot get %d bytes of shared memory", SMEM);
     configured = true;
   }
-  attention_decode_tma_kernel<HD><<<dim3(n_entries, a.nkv, a.nsplit), THREADS, SMEM, stream>>>(*mk, *mv, a);
+  launch_pdl(attention_decode_tma_kernel<HD>, dim3(n_entries, a.nkv, a.nsplit), dim3(THREADS), SMEM, stream, *mk,
+             *mv, a);
   return launched();
 }
 

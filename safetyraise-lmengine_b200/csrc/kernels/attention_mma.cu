@@ -234,6 +234,8 @@ attention_rows_kernel(const AttnArgs a) {
   bf16* kv_s = q_s + ROWS_PER_BLOCK * stride;            // [2 stages][K tile | V tile]
   const int tile_elems = KT * stride;
 
+  pdl_trigger();
+  pdl_wait();
   const int e = a.work[2 * blockIdx.x], rt = a.work[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -327,6 +329,8 @@ attention_keys_kernel(const AttnArgs a) {
   bf16* kv_s = q_s + 16 * stride;                           // [stages][K tile | V tile]
   const int tile_elems = KT * stride;
 
+  pdl_trigger();
+  pdl_wait();
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -467,7 +471,7 @@ static int launch_rows(const AttnArgs& a, int n_work, cudaStream_t stream) {
                          (ROWS_PER_BLOCK + 4 * KT) * (HD_MAX + 8) * 2);
     configured = true;
   }
-  attention_rows_kernel<HD_MAX><<<dim3(n_work, a.nkv), ATT_THREADS, smem, stream>>>(a);
+  launch_pdl(attention_rows_kernel<HD_MAX>, dim3(n_work, a.nkv), dim3(ATT_THREADS), smem, stream, a);
   return launched();
 }
 
@@ -481,7 +485,7 @@ static int launch_keys(const AttnArgs& a, int n_entries, cudaStream_t stream) {
                          (16 + 2 * KEYS_STAGES * KT) * (HD_MAX + 8) * 2);
     configured = true;
   }
-  attention_keys_kernel<HD_MAX><<<dim3(n_entries, a.nkv, a.nsplit), ATT_THREADS, smem, stream>>>(a);
+  launch_pdl(attention_keys_kernel<HD_MAX>, dim3(n_entries, a.nkv, a.nsplit), dim3(ATT_THREADS), smem, stream, a);
   return launched();
 }
 

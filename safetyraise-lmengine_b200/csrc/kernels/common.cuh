@@ -22,6 +22,31 @@ enum Status : int {
 
 int refuse(int code, const char* fmt, ...);   // records the text, returns code
 int launched();                                // cudaGetLastError() as a status
+bool pdl_enabled();                            // programmatic dependent launch on (default) or off
+
+// Launches a kernel that may begin before the kernel ahead of it in the stream has finished
+// (programmatic dependent launch).  Such a kernel must call pdl_wait() before it reads anything
+// an earlier kernel wrote or writes anything an earlier kernel reads; what it does before that
+// (barrier set-up, TMEM allocation, loads of weights, which no kernel writes) overlaps the
+// earlier kernel's tail.  pdl_trigger() lets the kernel behind start its own preamble.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 typedef __nv_bfloat16 bf16;
 

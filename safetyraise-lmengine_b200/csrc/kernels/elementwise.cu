@@ -11,6 +11,8 @@ namespace srlm {
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                     float* __restrict__ out, int H, int vocab, int* __restrict__ bad) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {          // the host checks too; never read outside the table
@@ -29,6 +31,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TA* __res
                                    const float* __restrict__ weight, float eps, TA* __restrict__ out,
                                    const int* __restrict__ rows, int H, int unit_offset) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* res = residual + src * H;
@@ -63,6 +67,8 @@ __device__ __forceinline__ float silu_f(float x) {
 // in[T, 2I]: gate in columns [0, I), up in [I, 2I)  ->  out[T, I]
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ in, TA* __restrict__ out, int I, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I, i = idx % I;
@@ -104,8 +110,8 @@ extern "C" int srlm_embed_gather(const int* ids, const void* table, int table_dt
   if (T <= 0) return ST_OK;
   if (H <= 0 || vocab <= 0) return refuse(ST_BAD_SIZE, "embed_gather: H=%d vocab=%d", H, vocab);
   const int block = H >= 1024 ? 256 : 128;
-  SRLM_DISPATCH_ACT(table_dtype, TW, (embed_gather_kernel<TW><<<T, block, 0, stream>>>(
-      ids, (const TW*)table, out, H, vocab, bad_flag)));
+  SRLM_DISPATCH_ACT(table_dtype, TW, launch_pdl(embed_gather_kernel<TW>, dim3(T), dim3(block), 0, stream,
+      ids, (const TW*)table, out, H, vocab, bad_flag));
   return launched();
 }
 
@@ -114,8 +120,8 @@ extern "C" int srlm_add_rmsnorm(float* residual, const void* delta, const float*
                                 cudaStream_t stream) {
   if (R <= 0) return ST_OK;
   if (H <= 0 || !(eps > 0.f)) return refuse(ST_BAD_SIZE, "add_rmsnorm: H=%d eps=%g", H, (double)eps);
-  SRLM_DISPATCH_ACT(act_dtype, TA, (add_rmsnorm_kernel<TA><<<R, norm_block(H), 0, stream>>>(
-      residual, (const TA*)delta, weight, eps, (TA*)out, rows, H, unit_offset)));
+  SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(add_rmsnorm_kernel<TA>, dim3(R), dim3(norm_block(H)), 0, stream,
+      residual, (const TA*)delta, weight, eps, (TA*)out, rows, H, unit_offset));
   return launched();
 }
 
@@ -123,8 +129,8 @@ extern "C" int srlm_swiglu(const void* in, void* out, int act_dtype, int T, int 
   if (T <= 0) return ST_OK;
   if (I <= 0) return refuse(ST_BAD_SIZE, "swiglu: I=%d", I);
   const size_t total = (size_t)T * I;
-  SRLM_DISPATCH_ACT(act_dtype, TA, (swiglu_kernel<TA><<<flat_grid(total, 256), 256, 0, stream>>>(
-      (const TA*)in, (TA*)out, I, total)));
+  SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(swiglu_kernel<TA>, dim3(flat_grid(total, 256)), dim3(256), 0, stream,
+      (const TA*)in, (TA*)out, I, total));
   return launched();
 }
 

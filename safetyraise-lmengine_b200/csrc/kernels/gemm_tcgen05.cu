@@ -21,6 +21,7 @@
 // src/artifact/mod.rs:377-405.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -77,6 +78,21 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+// The same load with an L2 eviction hint: weights are read once per step, so their lines should be
+// the first to go and leave the L2 to what is read again (activations) or was fetched ahead.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() {
@@ -171,6 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
   const int total_kb = (args.K + BK - 1) / BK;
@@ -197,13 +214,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
+      // Weights are written by no kernel, so the first stages' weight tiles are requested before the
+      // wait on the kernel ahead; the token tiles (its output) follow after it.
+      const int early = min(num_kb, STAGES);
+      const uint64_t stream_once = l2_policy_evict_first();
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full_bar[i], STAGE);
+        tma_load_2d_hint(smem + i * STAGE, &map_w, &full_bar[i], (kb_begin + i) * BK, n0, stream_once);
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem + i * STAGE + A_BYTES, &map_x, &full_bar[i], (kb_begin + i) * BK, m0);
+      for (int i = early; i < num_kb; ++i) {
         const int s = i % STAGES, j = i / STAGES;
         if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 1)) break;
         mbar_expect_tx(&full_bar[s], STAGE);
         uint8_t* a = smem + s * STAGE;
         const int k = (kb_begin + i) * BK;
-        tma_load_2d(a, &map_w, &full_bar[s], k, n0);
+        tma_load_2d_hint(a, &map_w, &full_bar[s], k, n0, stream_once);
         tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], k, m0);
       }
     }
@@ -230,6 +258,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     __syncwarp();
   } else {
+    pdl_wait();
     const bool ok = mbar_wait(accum_bar, 0, args.err_flag, 3);
     tcgen05_fence_after();
     const int lane_base = 32 * (warp & 3);              // the TMEM lanes this warp may read
@@ -371,7 +400,7 @@ static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& 
     configured = true;
   }
   dim3 grid((a.N + BM - 1) / BM, (a.M + BN - 1) / BN, splits);
-  gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, SMEM, stream>>>(*mw, *mx, a);
+  launch_pdl(gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, a);
   return launched();
 }
 
@@ -416,7 +445,13 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     // few stages per block so that three (two at 128 tokens) blocks share an SM: their prologues and
     // epilogues overlap one another's streaming, and tile counts that are no multiple of 148 still
     // keep every SM busy; the bytes in flight per SM stay the same
-    case 16: return launch<16, 4>(mw, mx, a, splits, stream);
+    case 16: {
+      static const int st16 = getenv("SRLM_GEMM_STAGES16") ? atoi(getenv("SRLM_GEMM_STAGES16")) : 4;
+      if (st16 == 2) return launch<16, 2>(mw, mx, a, splits, stream);
+      if (st16 == 8) return launch<16, 8>(mw, mx, a, splits, stream);
+      if (st16 == 12) return launch<16, 12>(mw, mx, a, splits, stream);
+      return launch<16, 4>(mw, mx, a, splits, stream);
+    }
     case 32: return launch<32, 3>(mw, mx, a, splits, stream);
     case 64: return launch<64, 3>(mw, mx, a, splits, stream);
     case 128: return launch<128, 3>(mw, mx, a, splits, stream);

@@ -13,6 +13,8 @@ namespace srlm {
 __global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cos_out,
                                   float* __restrict__ sin_out, int T, int half, double theta,
                                   int rotary_dim) {
+  pdl_trigger();
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   const int t = idx / half, i = idx % half;
@@ -34,6 +36,8 @@ __global__ void qk_norm_rope_append_kernel(
     float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     const int* __restrict__ kv_slot, int T, int nq, int nkv, int hd, int rotary_half,
     int heads_total, int write_kv, int page_size) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= T * heads_total) return;
@@ -89,8 +93,8 @@ extern "C" int srlm_rope_table(const int* positions, float* cos_out, float* sin_
   if (half <= 0 || rotary_dim != 2 * half || !(theta > 0.0))
     return refuse(ST_BAD_SIZE, "rope_table: rotary_dim=%d half=%d theta=%g", rotary_dim, half, theta);
   const int n = T * half;
-  rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, cos_out, sin_out, T, half, theta,
-                                                        rotary_dim);
+  launch_pdl(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, cos_out, sin_out, T, half,
+             theta, rotary_dim);
   return launched();
 }
 
@@ -111,8 +115,8 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
   const long long warps = (long long)T * heads_total;
   const int block = 128;
   const long long grid = (warps * 32 + block - 1) / block;
-  SRLM_DISPATCH_ACT(act_dtype, TA, (qk_norm_rope_append_kernel<TA, TA><<<(unsigned)grid, block, 0, stream>>>(
+  SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(qk_norm_rope_append_kernel<TA, TA>, dim3((unsigned)grid), dim3(block), 0, stream,
       (const TA*)qkv, (TA*)q_out, (TA*)k_cache, (TA*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t,
-      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv, page_size)));
+      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv, page_size));
   return launched();
 }

@@ -24,5 +24,14 @@ int launched() {
 }
 }  // namespace srlm
 
+namespace srlm {
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+}  // namespace srlm
+
+// 1: kernels of the forward pass may start before their predecessor in the stream has finished
+// (programmatic dependent launch, the default); 0: plain stream order.
+extern "C" void srlm_set_pdl(int on) { srlm::g_pdl = on != 0; }
+
 extern "C" const char* srlm_last_error() { return srlm::g_error; }
 extern "C" int srlm_kernels_abi() { return 1; }

@@ -57,7 +57,14 @@ class KernelLibrary:
             except Exception as e:   # noqa: BLE001
                 raise Unavailable(f"the CUDA kernel library is missing and could not be built: {e}") from e
             self._lib.srlm_last_error.restype = C.c_char_p
+            import os
+            if os.environ.get("SRLM_PDL", "1") == "0":     # plain stream order between kernels
+                self._lib.srlm_set_pdl(0)
         return self._lib
+
+    def set_pdl(self, on: bool) -> None:
+        """Programmatic dependent launch between the kernels of a step (on by default)."""
+        self.lib.srlm_set_pdl(C.c_int(1 if on else 0))
 
     def _check(self, status: int, what: str):
         self.launches += 1
