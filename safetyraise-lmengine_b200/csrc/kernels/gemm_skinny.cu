@@ -1,0 +1,160 @@
+// C[M,N] = X[M,K] . W[N,K]^T for M <= 16 tokens (decode): a weight-streaming
+// kernel.  Each block owns 16 weight rows; its 8 warps split K among them and
+// every lane pulls 16 bytes of a weight row straight from global memory into
+// registers, many loads in flight, no shared-memory staging and no barrier in
+// the loop.  The products run on the tensor cores with mma.sync m16n8k16: the
+// 16 weight rows are the M side, up to 8 tokens the N side (two tiles for up to
+// 16 tokens), float32 accumulation.  Because A and B may permute K in the same
+// way, a lane's 8 consecutive k values serve as the fragments of two k-steps, so
+// the global loads stay 16 bytes wide and whole 32-byte sectors are used.
+//
+// For a handful of tokens the product is bound by HBM alone; what matters is
+// that all SMs stream at once with little fixed cost per launch, which this
+// kernel does better than a TMA/TMEM pipeline sized for hundreds of tokens.
+// The eight warps' partial sums are added in warp order: the same on every run.
+//
+// Replaces, for decode, the same reference code as gemm_tcgen05.cu
+// (native/cuda/safetyraise_cuda.cu:43-63, src/artifact/mod.rs:377-405).
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_ROWS = 16;
+constexpr int SK_UNROLL = 4;
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {      // read once: do not keep in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {      // the tokens: read by every block
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, typename TO>     // MT token tiles of 8
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ C, int M, int N, int K,
+                   long long ldx, long long ldw, long long ldc) {
+  __shared__ float part[SK_WARPS][SK_ROWS][MT * 8 + 1];
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, q = lane & 3;
+  const int n0 = blockIdx.x * SK_ROWS;
+  // this warp's share of K, in groups of 32
+  const int groups = (K + 31) / 32;
+  const int per_warp = (groups + SK_WARPS - 1) / SK_WARPS;
+  const int g_lo = warp * per_warp, g_hi = min(groups, g_lo + per_warp);
+
+  const int row_a = min(n0 + r, N - 1), row_b = min(n0 + r + 8, N - 1);      // clamped: never stored if beyond N
+  const bf16* wa = W + (size_t)row_a * ldw + 8 * q;
+  const bf16* wb = W + (size_t)row_b * ldw + 8 * q;
+  const bf16* xs[MT];
+  bool x_ok[MT];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    const int m = t * 8 + r;                   // B fragment: column n = lane / 4 is the token
+    x_ok[t] = m < M;
+    xs[t] = X + (size_t)min(m, M - 1) * ldx + 8 * q;
+  }
+  float acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+
+  // Two batches of weight loads are kept in flight: the next batch is requested before the current
+  // one is multiplied.
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 a[2][SK_UNROLL], b[2][SK_UNROLL];
+  auto load_w = [&](int g, uint4 (&aa)[SK_UNROLL], uint4 (&bb)[SK_UNROLL]) {
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int k = (g + u) * 32;
+      const bool in = g + u < g_hi && k + 8 * q < K;        // K is a multiple of 8: a 16-byte piece is whole
+      aa[u] = in ? ld_stream16(wa + k) : zero;
+      bb[u] = in ? ld_stream16(wb + k) : zero;
+    }
+  };
+  load_w(g_lo, a[0], b[0]);
+  pdl_wait();
+  int buf = 0;
+  for (int g = g_lo; g < g_hi; g += SK_UNROLL, buf ^= 1) {
+    uint4 x[SK_UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int k = (g + u) * 32;
+      const bool in = g + u < g_hi && k + 8 * q < K;
+#pragma unroll
+      for (int t = 0; t < MT; ++t) x[u][t] = (in && x_ok[t]) ? ld_cached16(xs[t] + k) : zero;
+    }
+    if (buf == 0) load_w(g + SK_UNROLL, a[1], b[1]); else load_w(g + SK_UNROLL, a[0], b[0]);
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        // the lane's 8 consecutive k: pairs 0,1 are k-step 0 (columns c, c+8), pairs 2,3 are k-step 1
+        const uint4 av = buf == 0 ? a[0][u] : a[1][u], bv = buf == 0 ? b[0][u] : b[1][u];
+        mma_16816(acc[t], av.x, bv.x, av.y, bv.y, x[u][t].x, x[u][t].y);
+        mma_16816(acc[t], av.z, bv.z, av.w, bv.w, x[u][t].z, x[u][t].w);
+      }
+    }
+  }
+  // D fragment: rows r and r + 8, tokens 2q and 2q + 1 of each tile
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    part[warp][r][t * 8 + 2 * q] = acc[t][0];
+    part[warp][r][t * 8 + 2 * q + 1] = acc[t][1];
+    part[warp][r + 8][t * 8 + 2 * q] = acc[t][2];
+    part[warp][r + 8][t * 8 + 2 * q + 1] = acc[t][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < SK_ROWS * MT * 8; idx += SK_THREADS) {
+    const int m = idx / SK_ROWS, row = idx % SK_ROWS;       // consecutive threads: consecutive n
+    if (m < M && n0 + row < N) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) s += part[w][row][m];
+      C[(size_t)m * ldc + n0 + row] = from_float<TO>(s);
+    }
+  }
+}
+
+template <int MT, typename TO>
+static int launch_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                         long long ldc, cudaStream_t stream) {
+  // A plain launch (full stream order): measured on B200, letting this kernel start under its
+  // predecessor made whole decode steps slower, not faster.
+  gemm_skinny_kernel<MT, TO><<<dim3((N + SK_ROWS - 1) / SK_ROWS), dim3(SK_THREADS), 0, stream>>>(
+      (const bf16*)X, (const bf16*)W, (TO*)C, M, N, K, ldx, ldw, ldc);
+  return launched();
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+extern "C" int srlm_gemm_tn_skinny(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                   long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
+  if (M <= 0) return ST_OK;
+  if (M > 16) return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d; this kernel takes at most 16 tokens", M);
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < N)
+    return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
+  if (K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)X | (uintptr_t)W) & 15))
+    return refuse(ST_BAD_ALIGN, "gemm_skinny: K and the leading dimensions must be multiples of 8 and the operands "
+                  "16-byte aligned (16-byte loads)");
+  if (c_dtype == DT_BF16)
+    return M <= 8 ? launch_skinny<1, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, stream)
+                  : launch_skinny<2, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, stream);
+  if (c_dtype == DT_F32)
+    return M <= 8 ? launch_skinny<1, float>(X, W, C, M, N, K, ldx, ldw, ldc, stream)
+                  : launch_skinny<2, float>(X, W, C, M, N, K, ldx, ldw, ldc, stream);
+  return refuse(ST_BAD_DTYPE, "gemm_skinny: output dtype %d", c_dtype);
+}

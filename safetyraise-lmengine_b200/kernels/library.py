@@ -45,6 +45,11 @@ class KernelLibrary:
         self.launches = 0          # kernels launched through this object (a benchmark reports it)
         self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
         self.force_simt_attention = False
+        self.force_tcgen05_gemm = False
+        import os
+        # the weight-streaming kernel serves products of at most this many tokens and weight rows
+        self.skinny_max_tokens = int(os.environ.get("SRLM_SKINNY_TOKENS", "8"))
+        self.skinny_max_rows = int(os.environ.get("SRLM_SKINNY_ROWS", str(1 << 30)))
         self.force_cp_async_decode = False
 
     @property
@@ -193,13 +198,29 @@ class KernelLibrary:
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), C.c_int(splits),
             _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), _stream()), "gemm_tn_tcgen05")
 
+    def gemm_tn_skinny(self, a, w, out):
+        """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weight-streaming kernel of decode steps."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise ShapeError(f"gemm_skinny: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, "
+                             f"out {tuple(out.shape)}")
+        self._check(self.lib.srlm_gemm_tn_skinny(
+            _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
+            C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), _stream()),
+            "gemm_tn_skinny")
+
     def gemm(self, a, w, out):
         """The product path's matrix product: picks the kernel for the dtypes and sizes.  bfloat16
         operands go to the tensor cores; float32 operands, and widths that TMA cannot address
         (K not a multiple of 8), go to the float32 FMA kernel."""
         if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
                 and not self.force_simt_gemm):
-            self.gemm_tn_tcgen05(a, w, out)
+            if a.shape[0] <= self.skinny_max_tokens and w.shape[0] <= self.skinny_max_rows \
+                    and not self.force_tcgen05_gemm:
+                self.gemm_tn_skinny(a, w, out)          # a few tokens: bound by streaming the weights
+            else:
+                self.gemm_tn_tcgen05(a, w, out)
         else:
             self.gemm_tn_simt(a, w, out)
 

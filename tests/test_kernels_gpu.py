@@ -422,3 +422,36 @@ def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
     ops().paged_attention_decode_tma(q, kc, vc, out2, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
                                      part_o, part_ml)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 16, 8), (1, 4096, 4096), (8, 6144, 4096), (8, 200, 72), (5, 17, 520),
+                                     (9, 384, 96), (16, 4096, 12288), (13, 1000, 264), (8, 151936, 512)])
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
+def test_gemm_tn_skinny(M, N, K, odt):
+    g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, generator=g).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+    ops().gemm_tn_skinny(a, w, out)
+    ref = a.double() @ w.double().T
+    if odt == torch.float32:
+        assert torch.allclose(out.double(), ref, rtol=1e-4, atol=2e-4 * math.sqrt(K))
+    else:
+        assert torch.allclose(out.double(), ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    out2 = torch.empty_like(out)
+    ops().gemm_tn_skinny(a, w, out2)
+    assert torch.equal(out, out2)
+
+
+def test_gemm_skinny_finds_each_k_and_row():
+    K, N, M = 256, 256, 11
+    w = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
+    w[torch.arange(N), torch.arange(N) % K] = 1.0
+    a = (torch.arange(M * K, device=DEV).reshape(M, K) % 251).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    ops().gemm_tn_skinny(a, w, out)
+    assert torch.equal(out, a.float()[:, torch.arange(N, device=DEV) % K])
+    from safetyraise_lmengine_b200.errors import ShapeError
+    with pytest.raises(ShapeError):
+        ops().gemm_tn_skinny(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w,
+                             torch.empty(17, N, device=DEV, dtype=torch.float32))
