@@ -44,7 +44,7 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 template <int MT, typename TO>     // MT token tiles of 8
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ C, int M, int N, int K,
-                   long long ldx, long long ldw, long long ldc) {
+                   long long ldx, long long ldw, long long ldc, int swiglu8) {
   __shared__ float part[SK_WARPS][SK_ROWS][MT * 8 + 1];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,6 +116,20 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
     part[warp][r + 8][t * 8 + 2 * q + 1] = acc[t][3];
   }
   __syncthreads();
+  if (swiglu8) {
+    // the block's 16 rows are 8 gate rows then the 8 up rows of the same features: out = silu(gate) * up
+    for (int idx = threadIdx.x; idx < 8 * MT * 8; idx += SK_THREADS) {
+      const int m = idx / 8, row = idx % 8;
+      if (m < M && n0 + row + 8 < N) {
+        float gsum = 0.f, usum = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) { gsum += part[w][row][m]; usum += part[w][row + 8][m]; }
+        const float sg = gsum >= 0.f ? gsum / (1.f + expf(-gsum)) : gsum * (expf(gsum) / (1.f + expf(gsum)));
+        C[(size_t)m * ldc + (n0 >> 1) + row] = from_float<TO>(sg * usum);
+      }
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < SK_ROWS * MT * 8; idx += SK_THREADS) {
     const int m = idx / SK_ROWS, row = idx % SK_ROWS;       // consecutive threads: consecutive n
     if (m < M && n0 + row < N) {
@@ -129,11 +143,11 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
 
 template <int MT, typename TO>
 static int launch_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
-                         long long ldc, cudaStream_t stream) {
+                         long long ldc, int swiglu8, cudaStream_t stream) {
   // A plain launch (full stream order): measured on B200, letting this kernel start under its
   // predecessor made whole decode steps slower, not faster.
   gemm_skinny_kernel<MT, TO><<<dim3((N + SK_ROWS - 1) / SK_ROWS), dim3(SK_THREADS), 0, stream>>>(
-      (const bf16*)X, (const bf16*)W, (TO*)C, M, N, K, ldx, ldw, ldc);
+      (const bf16*)X, (const bf16*)W, (TO*)C, M, N, K, ldx, ldw, ldc, swiglu8);
   return launched();
 }
 
@@ -142,19 +156,21 @@ static int launch_skinny(const void* X, const void* W, void* C, int M, int N, in
 using namespace srlm;
 
 extern "C" int srlm_gemm_tn_skinny(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
-                                   long long ldx, long long ldw, long long ldc, cudaStream_t stream) {
+                                   long long ldx, long long ldw, long long ldc, int swiglu8, cudaStream_t stream) {
   if (M <= 0) return ST_OK;
+  if (swiglu8 && (N % 16 || ldc < N / 2))
+    return refuse(ST_BAD_SIZE, "gemm_skinny: the SwiGLU epilogue needs N=%d a multiple of 16 and ldc >= N/2", N);
   if (M > 16) return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d; this kernel takes at most 16 tokens", M);
-  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < N)
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || (!swiglu8 && ldc < N))
     return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
   if (K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)X | (uintptr_t)W) & 15))
     return refuse(ST_BAD_ALIGN, "gemm_skinny: K and the leading dimensions must be multiples of 8 and the operands "
                   "16-byte aligned (16-byte loads)");
   if (c_dtype == DT_BF16)
-    return M <= 8 ? launch_skinny<1, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, stream)
-                  : launch_skinny<2, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, stream);
+    return M <= 8 ? launch_skinny<1, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream)
+                  : launch_skinny<2, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream);
   if (c_dtype == DT_F32)
-    return M <= 8 ? launch_skinny<1, float>(X, W, C, M, N, K, ldx, ldw, ldc, stream)
-                  : launch_skinny<2, float>(X, W, C, M, N, K, ldx, ldw, ldc, stream);
+    return M <= 8 ? launch_skinny<1, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream)
+                  : launch_skinny<2, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream);
   return refuse(ST_BAD_DTYPE, "gemm_skinny: output dtype %d", c_dtype);
 }

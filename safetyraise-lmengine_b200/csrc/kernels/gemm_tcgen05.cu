@@ -167,7 +167,35 @@ struct GemmArgs {
   int kb_per_split;        // k blocks each split handles
   float* partial;          // [splits, M, N] float32 (split-K only)
   int* tile_counters;      // one per output tile, zero on entry (split-K only)
+  int swiglu8;             // 1: weight rows come in blocks of 16 (8 gate rows, then the 8 up rows of the same
+                           //    features); the output is silu(gate) * up, [M, N/2]
 };
+
+__device__ __forceinline__ float silu_stable(float x) {      // src/model/math.rs:11-22
+  if (x >= 0.f) return x / (1.f + expf(-x));
+  const float e = expf(x);
+  return x * (e / (1.f + e));
+}
+
+// Writes one finished accumulator value x = D[n, m].  Called by all 32 lanes of a warp together
+// (`valid` says whether this lane's element exists).
+__device__ __forceinline__ void store_result(const GemmArgs& args, int m, int n, float x, bool valid) {
+  if (args.swiglu8) {
+    const float other = __shfl_xor_sync(0xffffffffu, x, 8);     // the up row of this gate row, and back
+    if (valid && (n & 8) == 0) {
+      const float h = silu_stable(x) * other;
+      const size_t at = (size_t)m * args.ldc + (n >> 4) * 8 + (n & 7);
+      if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = h;
+      else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(h);
+    }
+    return;
+  }
+  if (valid) {
+    const size_t at = (size_t)m * args.ldc + n;
+    if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x;
+    else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x);
+  }
+}
 
 template <int BN>
 constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
@@ -271,16 +299,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         uint32_t v[CH];
         tmem_load<CH>(tmem_base + ((uint32_t)lane_base << 16) + c, v);
         tmem_load_wait();
-        if (n < args.N) {
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int m = m0 + c + j;
-            if (m < args.M) {
-              const float x = __uint_as_float(v[j]);
-              const size_t at = (size_t)m * args.ldc + n;
-              if (split) args.partial[((size_t)blockIdx.z * args.M + m) * args.N + n] = x;
-              else if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x;
-              else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x);
+        for (int j = 0; j < CH; ++j) {
+          const int m = m0 + c + j;
+          if (m < args.M) {                                  // the same for every lane
+            const float x = __uint_as_float(v[j]);
+            if (split) {
+              if (n < args.N) args.partial[((size_t)blockIdx.z * args.M + m) * args.N + n] = x;
+            } else {
+              store_result(args, m, n, x, n < args.N);
             }
           }
         }
@@ -298,27 +325,198 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (*last_flag) args.tile_counters[tile] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag && n < args.N) {
+      if (*last_flag) {
         __threadfence();
         const int rows = min(BN, args.M - m0), nz = (int)gridDim.z;
         const size_t slab = (size_t)args.M * args.N;
+        const bool have = n < args.N;
         for (int j = 0; j < rows; j += 4) {
           // four rows at a time: the loads of a row do not wait for the sums of the one before
           float x[4] = {0.f, 0.f, 0.f, 0.f};
-          for (int z = 0; z < nz; ++z) {
+          if (have) {
+            for (int z = 0; z < nz; ++z) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (j + u < rows) x[u] += __ldcg(&args.partial[z * slab + (size_t)(m0 + j + u) * args.N + n]);
+              for (int u = 0; u < 4; ++u)
+                if (j + u < rows) x[u] += __ldcg(&args.partial[z * slab + (size_t)(m0 + j + u) * args.N + n]);
+            }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (j + u < rows) {
-              const size_t at = (size_t)(m0 + j + u) * args.ldc + n;
-              if (args.c_is_f32) reinterpret_cast<float*>(args.C)[at] = x[u];
-              else reinterpret_cast<bf16*>(args.C)[at] = __float2bfloat16_rn(x[u]);
+          for (int u = 0; u < 4; ++u)
+            if (j + u < rows) store_result(args, m0 + j + u, n, x[u], have);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The persistent variant for many tokens (prefill): one block per SM walks over output tiles.  The
+// accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of a tile runs while
+// the MMAs of the next one are issued, and the shared-memory ring never drains between tiles.
+// The epilogue transposes each 32-token slab through shared memory and writes whole rows of C
+// (256 contiguous bytes per token and tile) instead of one element per lane.
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                               const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;
+  constexpr int SLAB = 32;                                   // tokens per epilogue slab
+  constexpr int SLAB_ROW = BM * 4 + 16;                      // bytes per token row of the slab (padded)
+  uint8_t* slab = smem + STAGES * STAGE;                     // [2][SLAB][SLAB_ROW]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(slab + 2 * SLAB * SLAB_ROW);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;                   // [2]
+  uint64_t* acc_empty = acc_full + 2;                        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (args.M + BN - 1) / BN, tiles_n = (args.N + BM - 1) / BM;
+  const int total_tiles = tiles_m * tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_wait();
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES, j = it / STAGES;
+          ok = mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 21);
+          if (!ok) break;
+          mbar_expect_tx(&full_bar[s], STAGE);
+          uint8_t* a = smem + s * STAGE;
+          tma_load_2d(a, &map_w, &full_bar[s], kb * BK, n0);
+          tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], kb * BK, m0);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16_f32(BN);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const int b = local & 1;
+        ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err_flag, 22);   // epilogue has drained it
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + b * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES, j = it / STAGES;
+          ok = mbar_wait(&full_bar[s], j & 1, args.err_flag, 23);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr), bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tcgen05_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          tcgen05_commit(&empty_bar[s]);
+        }
+        tcgen05_commit(&acc_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    pdl_wait();
+    const int ew = warp & 3;                               // TMEM lanes 32*ew .. 32*ew+31 belong to this warp
+    const int lane_base = 32 * ew;
+    const int tid_e = ew * 32 + lane;                      // 0..127 among the epilogue threads
+    const int out_cols = args.swiglu8 ? BM / 2 : BM;       // columns of C a tile produces
+    const int esize = args.c_is_f32 ? 4 : 2;
+    const bool vec_ok = (args.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
+    int local = 0, slab_turn = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      const int b = local & 1;
+      const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
+      ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err_flag, 24);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int c0 = args.swiglu8 ? n0 / 2 : n0;           // first column of C of this tile
+#pragma unroll 1
+      for (int c = 0; c < BN; c += SLAB, slab_turn ^= 1) {
+        uint32_t v[SLAB];
+        tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
+        tmem_load_wait();
+        if (c + SLAB >= BN) {                               // everything of this tile has left TMEM
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+        }
+        if (m0 + c >= args.M) continue;                     // slab beyond the last token (same for all warps)
+        uint8_t* sl = slab + slab_turn * SLAB * SLAB_ROW;
+        // D[n, m] -> slab[m][column of C]
+#pragma unroll
+        for (int j = 0; j < SLAB; ++j) {
+          float x = __uint_as_float(v[j]);
+          int col = lane_base + lane;
+          bool keep = true;
+          if (args.swiglu8) {
+            const float other = __shfl_xor_sync(0xffffffffu, x, 8);
+            keep = (lane & 8) == 0;
+            x = silu_stable(x) * other;
+            col = (lane_base >> 1) + (lane >> 4) * 8 + (lane & 7);
+          }
+          if (keep) {
+            if (args.c_is_f32) *reinterpret_cast<float*>(sl + j * SLAB_ROW + col * 4) = x;
+            else *reinterpret_cast<bf16*>(sl + j * SLAB_ROW + col * 2) = __float2bfloat16_rn(x);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // rows of the slab -> C, 16 bytes per thread
+        const int row_bytes = out_cols * esize;
+        const int vec_per_row = row_bytes / 16;
+        const int n_limit = (args.swiglu8 ? args.N / 2 : args.N) - c0;     // valid columns in this tile
+        for (int idx = tid_e; idx < SLAB * vec_per_row; idx += 128) {
+          const int j = idx / vec_per_row, vcol = idx % vec_per_row;
+          const int m = m0 + c + j;
+          if (m >= args.M) continue;
+          const int col = vcol * (16 / esize);              // first column of this 16-byte piece
+          uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)m * args.ldc + c0 + col) * esize;
+          const uint8_t* src = sl + j * SLAB_ROW + vcol * 16;
+          if (vec_ok && col + 16 / esize <= n_limit) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+          } else {
+            for (int e = 0; e < 16 / esize && col + e < n_limit; ++e) {
+              if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = reinterpret_cast<const float*>(src)[e];
+              else reinterpret_cast<bf16*>(dst)[e] = reinterpret_cast<const bf16*>(src)[e];
             }
           }
         }
+        // the other slab buffer is used next; this one is rewritten two slabs later, after another barrier
       }
     }
   }
@@ -404,6 +602,26 @@ static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& 
   return launched();
 }
 
+template <int BN, int STAGES>
+static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * stage_bytes<BN>() + 2 * 32 * (BM * 4 + 16) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return refuse((int)e, "gemm_tcgen05: cannot get %d bytes of shared memory", SMEM);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int tiles = ((a.N + BM - 1) / BM) * ((a.M + BN - 1) / BN);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  launch_pdl(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, a);
+  return launched();
+}
+
 }  // namespace srlm
 
 using namespace srlm;
@@ -412,10 +630,11 @@ using namespace srlm;
 // at the start; float32 partials [splits, M, N] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
 extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                     long long ldx, long long ldw, long long ldc, int splits, void* workspace,
-                                    long long workspace_bytes, int* err_flag, cudaStream_t stream) {
+                                    long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
   if (M <= 0) return ST_OK;
-  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < N)
-    return refuse(ST_BAD_SIZE, "gemm_tcgen05: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < (swiglu8 ? N / 2 : N) || (swiglu8 && N % 16))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld swiglu8=%d", M, N, K, ldx,
+                  ldw, ldc, swiglu8);
   if (K % 8 || ldx % 8 || ldw % 8)
     return refuse(ST_BAD_SIZE, "gemm_tcgen05: K=%d and the leading dimensions must be multiples of 8 "
                   "(TMA rows start on 16-byte boundaries)", K);
@@ -428,7 +647,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   int kb_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr};
+  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0};
   if (splits > 1) {
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     const long long need = 65536 + (long long)splits * M * N * 4;
@@ -441,6 +660,10 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   const CUtensorMap* mw = cached_map(W, N, K, ldw, BM, true);
   const CUtensorMap* mx = cached_map(X, M, K, ldx, bn, false);
   if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
+  if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel
+    static const bool off = getenv("SRLM_GEMM_PERSISTENT") && !atoi(getenv("SRLM_GEMM_PERSISTENT"));
+    if (!off) return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, stream) : launch_persistent<256, 4>(mw, mx, a, stream);
+  }
   switch (bn) {
     // few stages per block so that three (two at 128 tokens) blocks share an SM: their prologues and
     // epilogues overlap one another's streaming, and tile counts that are no multiple of 148 still

@@ -183,11 +183,14 @@ class KernelLibrary:
                 best, best_eff = s, eff
         return best
 
-    def gemm_tn_tcgen05(self, a, w, out, splits=None):
-        """out[M,N] = a[M,K] @ w[N,K]^T, bfloat16 operands, tcgen05 tensor cores, float32 accumulation."""
+    def gemm_tn_tcgen05(self, a, w, out, splits=None, swiglu8=False):
+        """out[M,N] = a[M,K] @ w[N,K]^T, bfloat16 operands, tcgen05 tensor cores, float32 accumulation.
+        swiglu8: w's rows come in blocks of 16 (8 gate rows, then the 8 up rows of the same features)
+        and out[M, N/2] = silu(gate) * up."""
         M, K = a.shape
         N = w.shape[0]
-        if w.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        if (w.shape[1] != K or tuple(out.shape) != (M, N // 2 if swiglu8 else N) or a.dtype != torch.bfloat16
+                or w.dtype != torch.bfloat16):
             raise ShapeError(f"gemm_tcgen05: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, "
                              f"out {tuple(out.shape)}")
         ws, err = self._gemm_state(a.device)
@@ -196,21 +199,28 @@ class KernelLibrary:
         self._check(self.lib.srlm_gemm_tn_tcgen05(
             _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), C.c_int(splits),
-            _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), _stream()), "gemm_tn_tcgen05")
+            _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()), "gemm_tn_tcgen05")
 
-    def gemm_tn_skinny(self, a, w, out):
-        """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weight-streaming kernel of decode steps."""
+    def gemm_tn_skinny(self, a, w, out, swiglu8=False):
+        """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weight-streaming kernel of decode steps.
+        swiglu8: as in gemm_tn_tcgen05."""
         M, K = a.shape
         N = w.shape[0]
-        if w.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        if (w.shape[1] != K or tuple(out.shape) != (M, N // 2 if swiglu8 else N) or a.dtype != torch.bfloat16
+                or w.dtype != torch.bfloat16):
             raise ShapeError(f"gemm_skinny: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, "
                              f"out {tuple(out.shape)}")
         self._check(self.lib.srlm_gemm_tn_skinny(
             _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
-            C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), _stream()),
-            "gemm_tn_skinny")
+            C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)),
+            C.c_int(int(swiglu8)), _stream()), "gemm_tn_skinny")
 
-    def gemm(self, a, w, out):
+    def can_fuse_swiglu(self, a_dtype, w) -> bool:
+        """Whether gemm(..., swiglu8=True) is offered for these operands (the tensor-core kernels only)."""
+        return (a_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
+                and w.shape[0] % 16 == 0 and not self.force_simt_gemm)
+
+    def gemm(self, a, w, out, swiglu8=False):
         """The product path's matrix product: picks the kernel for the dtypes and sizes.  bfloat16
         operands go to the tensor cores; float32 operands, and widths that TMA cannot address
         (K not a multiple of 8), go to the float32 FMA kernel."""
@@ -218,10 +228,12 @@ class KernelLibrary:
                 and not self.force_simt_gemm):
             if a.shape[0] <= self.skinny_max_tokens and w.shape[0] <= self.skinny_max_rows \
                     and not self.force_tcgen05_gemm:
-                self.gemm_tn_skinny(a, w, out)          # a few tokens: bound by streaming the weights
+                self.gemm_tn_skinny(a, w, out, swiglu8)          # a few tokens: bound by streaming the weights
             else:
-                self.gemm_tn_tcgen05(a, w, out)
+                self.gemm_tn_tcgen05(a, w, out, swiglu8=swiglu8)
         else:
+            if swiglu8:
+                raise ShapeError("the fused SwiGLU epilogue exists in the bfloat16 tensor-core kernels only")
             self.gemm_tn_simt(a, w, out)
 
     def paged_attention_rows(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv, hd,

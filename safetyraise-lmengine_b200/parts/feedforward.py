@@ -21,9 +21,19 @@ class GatedDense(Part):
             raise Unsupported(f"activation {spec.activation!r} is not implemented")
         self.spec = spec
         p = prefix + "mlp."
-        # gate rows then up rows: one projection whose output the SwiGLU kernel halves
-        self.gate_up = Linear(torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]],
-                                        dim=0).contiguous(), p + "gate_up")
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        I, H = gate.shape
+        # One projection for gate and up.  For the tensor-core kernels the rows are interleaved in
+        # blocks of 16 (8 gate rows, then the 8 up rows of the same features) so that the product's
+        # epilogue holds both halves of a feature and writes silu(gate) * up directly; otherwise gate
+        # rows then up rows, and a SwiGLU kernel halves the output.
+        self.fused = (I % 8 == 0 and gate.dtype == torch.bfloat16 and mctx.dtype == torch.bfloat16
+                      and H % 8 == 0 and not mctx.options.get("unfused_swiglu", False))
+        if self.fused:
+            w = torch.stack([gate.view(I // 8, 8, H), up.view(I // 8, 8, H)], dim=1).reshape(2 * I, H)
+        else:
+            w = torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(w.contiguous(), p + "gate_up")
         self.down = Linear(tensors[p + "down_proj.weight"], p + "down_proj")
 
     @classmethod
@@ -34,7 +44,10 @@ class GatedDense(Part):
                 TensorDecl(p + "down_proj.weight", (spec.hidden_size, spec.intermediate_size), MATRIX)]
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        gu = self.gate_up(ctx, x, "ffn.gate_up")
         h = ctx.workspace.get("ffn.h", x.shape[0], self.spec.intermediate_size, ctx.dtype)
-        ops.swiglu(gu, h)
+        if self.fused and ops.can_fuse_swiglu(x.dtype, self.gate_up.weight):
+            ops.gemm(x, self.gate_up.weight, h, swiglu8=True)
+        else:
+            gu = self.gate_up(ctx, x, "ffn.gate_up")
+            ops.swiglu(gu, h)
         return self.down(ctx, h, "ffn.down")

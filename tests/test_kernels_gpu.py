@@ -455,3 +455,27 @@ def test_gemm_skinny_finds_each_k_and_row():
     with pytest.raises(ShapeError):
         ops().gemm_tn_skinny(torch.zeros(17, K, device=DEV, dtype=torch.bfloat16), w,
                              torch.empty(17, N, device=DEV, dtype=torch.float32))
+
+
+@pytest.mark.parametrize("M, I, K, splits", [(1, 8, 64, 1), (8, 12288, 512, 1), (5, 24, 72, 1), (16, 256, 96, 1),
+                                             (33, 128, 256, 2), (100, 4096, 512, 1), (64, 512, 2048, 3), (300, 200, 128, 1)])
+def test_gemm_with_fused_swiglu(M, I, K, splits):
+    """Both tensor-core products with the SwiGLU epilogue against product-then-SwiGLU."""
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(I, K, device=DEV, generator=g) / math.sqrt(K) * 2).to(torch.bfloat16)
+    up = (torch.randn(I, K, device=DEV, generator=g) / math.sqrt(K) * 2).to(torch.bfloat16)
+    w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    gd, ud = a.double() @ gate.double().T, a.double() @ up.double().T
+    ref = gd * torch.sigmoid(gd) * ud
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops().gemm_tn_tcgen05(a, w, out, splits=splits, swiglu8=True)
+    assert ops().gemm_error_flag(a.device) == 0
+    assert torch.allclose(out.double(), ref, rtol=2e-2, atol=2e-2)
+    if M <= 16:
+        out2 = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops().gemm_tn_skinny(a, w, out2, swiglu8=True)
+        assert torch.allclose(out2.double(), ref, rtol=2e-2, atol=2e-2)
+        out32 = torch.full((M, I), float("nan"), device=DEV, dtype=torch.float32)
+        ops().gemm_tn_skinny(a, w, out32, swiglu8=True)
+        assert torch.allclose(out32.double(), ref, rtol=1e-3, atol=1e-3)
