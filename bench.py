@@ -255,6 +255,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-extras", action="store_true", help="only the default decode measurement")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
+    ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -270,6 +271,10 @@ def main() -> int:
     big = max(64, B)
     eng = build_engine(args.layers, max_requests=big, tokens_in_cache=big * (CONTEXT + 256) + PREFILL_TOKENS,
                        max_batch_tokens=PREFILL_TOKENS, graphs=not args.no_graphs)
+    if args.only_prefill:
+        pf_ms = time_prefill(eng, PREFILL_TOKENS, 2)
+        print(json.dumps({"prefill_ms": pf_ms, "tokens": PREFILL_TOKENS}))
+        return 0
     slots = fill_contexts(eng, B, CONTEXT)
     with ClockSampler() as clocks:
         ms, launches = time_decode(eng, slots, args.steps, args.warmup)

@@ -377,6 +377,237 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 }
 
 // ---------------------------------------------------------------------------
+// Rows-split attention with the same TMA page loads, for many rows per entry (prefill, mixed
+// batches): a block takes 128 rows (query tokens x query heads of one KV group) of one entry and
+// one KV head; eight consumer warps of 16 rows each share the key/value tiles that the producer
+// thread brings in; every warp keeps its rows' whole output in registers.
+// ---------------------------------------------------------------------------
+constexpr int ROWS_CONSUMERS = 8;
+constexpr int ROWS_STAGES = 3;           // one block per SM (its registers fill the SM): a deeper ring instead
+constexpr int ROWS_THREADS = (ROWS_CONSUMERS + 1) * 32;
+constexpr int ROWS_PER_BLOCK = ROWS_CONSUMERS * 16;
+
+struct RowsArgs {
+  const bf16* q;
+  bf16* out;
+  const int* block_table;
+  int table_stride;
+  const int* cu_q;
+  const int* kv_lens;
+  const int* work;            // (entry, tile of 128 rows) pairs
+  int nq, nkv, hd, page_size;
+  float scale_log2;
+  int window;
+  int* err_flag;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ROWS_THREADS, 1)
+attention_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                          const RowsArgs a) {
+  constexpr int PANELS = HD / 64;
+  constexpr int TILE_BYTES = KT * HD * 2;
+  constexpr int KS = HD / 16;
+  constexpr int NT_O = HD / 8;
+  extern __shared__ uint8_t dec_smem_raw[];
+  uint8_t* smem = dec_smem_raw + ((1024u - (s32(dec_smem_raw) & 1023u)) & 1023u);
+  uint8_t* tiles = smem;                                                  // [ROWS_STAGES][K tile | V tile]
+  bf16* q_s = reinterpret_cast<bf16*>(smem + ROWS_STAGES * 2 * TILE_BYTES);    // [128][HD + 8]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(q_s + ROWS_PER_BLOCK * (HD + 8));
+  uint64_t* empty_bar = full_bar + ROWS_STAGES;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ROWS_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ROWS_CONSUMERS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  pdl_wait();
+  const int e = a.work[2 * blockIdx.x], rt = a.work[2 * blockIdx.x + 1], kvh = blockIdx.y;
+  const int g = a.nq / a.nkv;
+  const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
+  const int rows_total = q_len * g;
+  const int* table = a.block_table + (size_t)e * a.table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int r_first = rt * ROWS_PER_BLOCK;
+  const int r_last = min(rows_total, r_first + ROWS_PER_BLOCK) - 1;
+  const int n_keys = start + r_last / g + 1;                             // keys the last row sees
+  const int pos_first = start + r_first / g;
+  const int first_key = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+  const int jb0 = (first_key / KT) * KT;
+  const int n_tiles = (n_keys - jb0 + KT - 1) / KT;
+
+  for (int idx = threadIdx.x; idx < ROWS_PER_BLOCK * (HD / 8); idx += ROWS_THREADS) {
+    const int row = idx / (HD / 8), c = idx % (HD / 8);
+    const int r = r_first + row;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows_total)
+      v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + r / g) * a.nq + kvh * g + r % g) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * (HD + 8) + c * 8) = v;
+  }
+  __syncthreads();
+
+  if (warp == ROWS_CONSUMERS) {
+    if (lane == 0) {
+      const int ps = a.page_size;
+      const int box_rows = ps < KT ? ps : KT;
+      const int boxes = KT / box_rows;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % ROWS_STAGES, j = t / ROWS_STAGES;
+        if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, a.err_flag, 31)) break;
+        mbar_expect_tx(&full_bar[s], 2 * TILE_BYTES);
+        uint8_t* kt = tiles + s * 2 * TILE_BYTES;
+        uint8_t* vt = kt + TILE_BYTES;
+        const int jb = jb0 + t * KT;
+        for (int b = 0; b < boxes; ++b) {
+          const int key = jb + b * box_rows;
+          const int pg = key / ps;
+          const int page = (pg < a.table_stride && key < kv_len) ? max(table[pg], 0) : 0;
+          const int row = (page * a.nkv + kvh) * ps + key % ps;
+#pragma unroll
+          for (int p = 0; p < PANELS; ++p) {
+            tma_load_2d(kt + p * (KT * 128) + b * box_rows * 128, &map_k, &full_bar[s], p * 64, row);
+            tma_load_2d(vt + p * (KT * 128) + b * box_rows * 128, &map_v, &full_bar[s], p * 64, row);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    return;
+  }
+
+  // ---------------- consumers: 16 rows each ----------------
+  const int mi = lane >> 3;
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int row = warp * 16 + (mi & 1) * 8 + (lane & 7);
+    ldsm4(qf[ks], s32(q_s + row * (HD + 8) + (ks * 2 + (mi >> 1)) * 8));
+  }
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+  const int ra = r_first + warp * 16 + (lane >> 2), rb = ra + 8;
+  const int pos0 = start + min(ra, rows_total - 1) / g, pos1 = start + min(rb, rows_total - 1) / g;
+  const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+  const int warp_pos_max = start + min(r_first + warp * 16 + 15, rows_total - 1) / g;
+  const int warp_pos_min = start + min(r_first + warp * 16, rows_total - 1) / g;
+  const int warp_lo = a.window > 0 ? max(0, warp_pos_max - a.window + 1) : 0;   // first key any row of the warp sees... of its last row
+  const int warp_lo_min = a.window > 0 ? max(0, warp_pos_min - a.window + 1) : 0;
+  const bool warp_live = r_first + warp * 16 < rows_total;
+
+  bool ok = true;
+  for (int t = 0; t < n_tiles && ok; ++t) {
+    const int s = t % ROWS_STAGES, j = t / ROWS_STAGES;
+    ok = mbar_wait(&full_bar[s], j & 1, a.err_flag, 32);
+    if (!ok) break;
+    const uint32_t kt = s32(tiles + s * 2 * TILE_BYTES), vt = kt + TILE_BYTES;
+    const int jb = jb0 + t * KT;
+    if (jb + KT > kv_len || (a.window > 0 && jb < first_key)) {
+      // rows of the V tile that hold no key of this request may contain anything; a zero weight times
+      // a non-finite value would poison the sum.  Every warp clears them all (the same zeros) before it reads.
+      const int bad_from = jb + KT > kv_len ? kv_len - jb : KT;
+      const int bad_to = (a.window > 0 && jb < first_key) ? first_key - jb : 0;
+      for (int idx = lane; idx < KT * (HD / 8); idx += 32) {
+        const int key = idx / (HD / 8), c16 = idx % (HD / 8);
+        if (key >= bad_from || key < bad_to)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(tile_addr(vt, key, c16)), "r"(0) : "memory");
+      }
+      __syncwarp();
+    }
+    if (warp_live && jb <= warp_pos_max && jb + KT > warp_lo_min) {
+      float sc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int nt = 0; nt < 8; nt += 2) {
+          uint32_t b[4];
+          ldsm4(b, tile_addr(kt, (nt + (mi >> 1)) * 8 + (lane & 7), ks * 2 + (mi & 1)));
+          mma16816(sc[nt], qf[ks], b[0], b[1]);
+          mma16816(sc[nt + 1], qf[ks], b[2], b[3]);
+        }
+      }
+      // a tile needs the mask unless every key of it is visible to every row of the warp
+      const bool need_mask = jb + KT - 1 > warp_pos_min || jb < warp_lo || jb + KT > n_keys;
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float v = sc[nt][x] * a.scale_log2;
+          if (need_mask) {
+            const int key = jb + nt * 8 + (lane & 3) * 2 + (x & 1);
+            const int pos = x < 2 ? pos0 : pos1, lo = x < 2 ? lo0 : lo1;
+            if (key > pos || key < lo) v = -CUDART_INF_F;
+          }
+          sc[nt][x] = v;
+          if (x < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float base0 = mn0 == -CUDART_INF_F ? 0.f : mn0, base1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);
+      m0 = mn0;
+      m1 = mn1;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pf[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const float p0 = exp2f(sc[nt][0] - base0), p1 = exp2f(sc[nt][1] - base0);
+        const float p2 = exp2f(sc[nt][2] - base1), p3 = exp2f(sc[nt][3] - base1);
+        sum0 += p0 + p1;
+        sum1 += p2 + p3;
+        pf[nt >> 1][(nt & 1) * 2 + 0] = pack2(p0, p1);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p2, p3);
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * alpha0 + sum0;
+      l1 = l1 * alpha1 + sum1;
+#pragma unroll
+      for (int dn = 0; dn < NT_O; ++dn) {
+        o[dn][0] *= alpha0; o[dn][1] *= alpha0; o[dn][2] *= alpha1; o[dn][3] *= alpha1;
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+        for (int dn = 0; dn < NT_O; dn += 2) {
+          uint32_t b[4];
+          ldsm4_t(b, tile_addr(vt, kk * 16 + (mi & 1) * 8 + (lane & 7), dn + (mi >> 1)));
+          mma16816(o[dn], pf[kk], b[0], b[1]);
+          mma16816(o[dn + 1], pf[kk], b[2], b[3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+  }
+  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+  for (int dn = 0; dn < NT_O; ++dn) {
+    const int d = dn * 8 + (lane & 3) * 2;
+    if (ra < rows_total)
+      *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + ra / g) * a.nq + kvh * g + ra % g) * HD + d) =
+          pack2(o[dn][0] * inv0, o[dn][1] * inv0);
+    if (rb < rows_total)
+      *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + rb / g) * a.nq + kvh * g + rb % g) * HD + d) =
+          pack2(o[dn][2] * inv1, o[dn][3] * inv1);
+  }
+}
+
+// ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -435,6 +666,20 @@ static int launch(const CUtensorMap* mk, const CUtensorMap* mv, const Args& a, i
   return launched();
 }
 
+template <int HD>
+static int launch_rows(const CUtensorMap* mk, const CUtensorMap* mv, const RowsArgs& a, int n_work, cudaStream_t stream) {
+  constexpr int SMEM = ROWS_STAGES * 2 * KT * HD * 2 + ROWS_PER_BLOCK * (HD + 8) * 2 + 2 * ROWS_STAGES * 8 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_rows_tma_kernel<HD>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (err != cudaSuccess) return refuse((int)err, "attention_rows_tma: cannot get %d bytes of shared memory", SMEM);
+    configured = true;
+  }
+  launch_pdl(attention_rows_tma_kernel<HD>, dim3(n_work, a.nkv), dim3(ROWS_THREADS), SMEM, stream, *mk, *mv, a);
+  return launched();
+}
+
 }  // namespace dec
 }  // namespace srlm
 
@@ -473,4 +718,24 @@ extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cach
     case 192: return dec::launch<192>(mk, mv, a, n_entries, stream);
     default: return dec::launch<256>(mk, mv, a, n_entries, stream);
   }
+}
+
+// Ragged batch with TMA page loads.  work: n_work pairs (entry, tile of 128 rows); an entry with q tokens has
+// ceil(q * (nq/nkv) / 128) tiles.  Same size rules as srlm_paged_attention_decode_tma (head_dim 64 or 128 here).
+extern "C" int srlm_paged_attention_rows_tma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             long long num_pages, const int* block_table, int table_stride,
+                                             const int* cu_q, const int* kv_lens, const int* work, int n_work, int nq,
+                                             int nkv, int hd, int page_size, float scale, int window, int* err_flag,
+                                             cudaStream_t stream) {
+  if (n_work <= 0) return ST_OK;
+  if (!srlm_attention_decode_tma_takes(hd, page_size) || hd > 128 || nq <= 0 || nkv <= 0 || nq % nkv)
+    return refuse(ST_BAD_SIZE, "attention_rows_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
+  const int box_rows = page_size < dec::KT ? page_size : dec::KT;
+  const long long rows = num_pages * nkv * page_size;
+  const CUtensorMap* mk = dec::cache_map(k_cache, rows, hd, box_rows);
+  const CUtensorMap* mv = dec::cache_map(v_cache, rows, hd, box_rows);
+  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_rows_tma: cuTensorMapEncodeTiled refused the cache");
+  dec::RowsArgs a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, hd, page_size,
+                  scale * 1.4426950408889634f, window, err_flag};
+  return hd == 64 ? dec::launch_rows<64>(mk, mv, a, n_work, stream) : dec::launch_rows<128>(mk, mv, a, n_work, stream);
 }

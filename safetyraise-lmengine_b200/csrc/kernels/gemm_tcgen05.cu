@@ -171,10 +171,14 @@ struct GemmArgs {
                            //    features); the output is silu(gate) * up, [M, N/2]
 };
 
-__device__ __forceinline__ float silu_stable(float x) {      // src/model/math.rs:11-22
-  if (x >= 0.f) return x / (1.f + expf(-x));
-  const float e = expf(x);
-  return x * (e / (1.f + e));
+// x * logistic(x) (src/model/math.rs:11-22) in float32 with the fast exponential and reciprocal:
+// one branch-free form serves both signs here, since exp2 of a large argument is +inf and its
+// reciprocal 0 (x -> -inf gives -0, as the stable form does); relative error ~1e-6.
+__device__ __forceinline__ float silu_stable(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return x * r;
 }
 
 // Writes one finished accumulator value x = D[n, m].  Called by all 32 lanes of a warp together
@@ -479,18 +483,25 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         if (m0 + c >= args.M) continue;                     // slab beyond the last token (same for all warps)
         uint8_t* sl = slab + slab_turn * SLAB * SLAB_ROW;
         // D[n, m] -> slab[m][column of C]
+        if (args.swiglu8) {
+          // lanes l and l^8 hold the gate and the up row of one feature; they share the work: the
+          // gate lane finishes the even token of a pair, the up lane the odd one
+          const bool gate_lane = (lane & 8) == 0;
+          const int col = (lane_base >> 1) + (lane >> 4) * 8 + (lane & 7);
 #pragma unroll
-        for (int j = 0; j < SLAB; ++j) {
-          float x = __uint_as_float(v[j]);
-          int col = lane_base + lane;
-          bool keep = true;
-          if (args.swiglu8) {
-            const float other = __shfl_xor_sync(0xffffffffu, x, 8);
-            keep = (lane & 8) == 0;
-            x = silu_stable(x) * other;
-            col = (lane_base >> 1) + (lane >> 4) * 8 + (lane & 7);
+          for (int j = 0; j < SLAB; j += 2) {
+            const float mine0 = __uint_as_float(v[j]), mine1 = __uint_as_float(v[j + 1]);
+            const float got = __shfl_xor_sync(0xffffffffu, gate_lane ? mine1 : mine0, 8);
+            const float hval = gate_lane ? silu_stable(mine0) * got : silu_stable(got) * mine1;
+            const int row = gate_lane ? j : j + 1;
+            if (args.c_is_f32) *reinterpret_cast<float*>(sl + row * SLAB_ROW + col * 4) = hval;
+            else *reinterpret_cast<bf16*>(sl + row * SLAB_ROW + col * 2) = __float2bfloat16_rn(hval);
           }
-          if (keep) {
+        } else {
+#pragma unroll
+          for (int j = 0; j < SLAB; ++j) {
+            const float x = __uint_as_float(v[j]);
+            const int col = lane_base + lane;
             if (args.c_is_f32) *reinterpret_cast<float*>(sl + j * SLAB_ROW + col * 4) = x;
             else *reinterpret_cast<bf16*>(sl + j * SLAB_ROW + col * 2) = __float2bfloat16_rn(x);
           }

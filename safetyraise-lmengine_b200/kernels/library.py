@@ -244,6 +244,16 @@ class KernelLibrary:
             _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]), C.c_int(nq), C.c_int(nkv), C.c_int(hd),
             C.c_int(page_size), C.c_float(scale), C.c_int(window or 0), _stream()), "paged_attention_rows")
 
+    def paged_attention_rows_tma(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv, hd,
+                                 page_size, scale, window=0):
+        """Rows-split attention with TMA page loads; work: int32 [n, 2] (entry, tile of 128 rows)."""
+        err = self._gemm_state(q.device)[1]
+        self._check(self.lib.srlm_paged_attention_rows_tma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+            C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
+            C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+            _ptr(err), _stream()), "paged_attention_rows_tma")
+
     def paged_attention_keys(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv, hd,
                              page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
         """bfloat16 tensor-core attention when every entry has at most 16 rows (decode); keys in nsplit slices."""
@@ -322,13 +332,24 @@ class KernelLibrary:
             self.paged_attention_keys(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries,
                                       nq, nkv, hd, page_size, scale, window, chunk, nsplit, part_o, part_ml)
             return
-        work = ctx.tables.get(("attention_rows_work", g))
+        tma = (hd in (64, 128) and self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))
+               and not self.force_cp_async_decode)
+        rows_per_tile = 128 if tma else 64
+        work = ctx.tables.get(("attention_rows_work", g, rows_per_tile))
         if work is None:
-            pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"]) for t in range((ql * g + 63) // 64)]
+            # the last row tiles of an entry see the most keys: they go first, so that the long blocks
+            # do not start when the short ones have already left the GPU half empty
+            pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"])
+                     for t in reversed(range((ql * g + rows_per_tile - 1) // rows_per_tile))]
+            pairs.sort(key=lambda et: -(ctx.host["starts"][et[0]] + (et[1] + 1) * rows_per_tile // g))
             work = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(q.device, non_blocking=True)
-            ctx.tables[("attention_rows_work", g)] = work
-        self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq, nkv, hd,
-                                  page_size, scale, window)
+            ctx.tables[("attention_rows_work", g, rows_per_tile)] = work
+        if tma:
+            self.paged_attention_rows_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq,
+                                          nkv, hd, page_size, scale, window)
+        else:
+            self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq, nkv,
+                                      hd, page_size, scale, window)
 
     # ---- sampling -------------------------------------------------------------
     def argmax(self, logits, out_tokens, bad_flag):

@@ -479,3 +479,32 @@ def test_gemm_with_fused_swiglu(M, I, K, splits):
         out32 = torch.full((M, I), float("nan"), device=DEV, dtype=torch.float32)
         ops().gemm_tn_skinny(a, w, out32, swiglu8=True)
         assert torch.allclose(out32.double(), ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("nq, nkv, hd, ps", [(32, 8, 128, 16), (8, 2, 64, 16), (4, 4, 64, 8), (16, 1, 128, 32),
+                                             (6, 2, 128, 64)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_paged_attention_rows_tma(nq, nkv, hd, ps, window):
+    lens_q, lens_kv = [1, 7, 33, 1, 2, 150, 300], [1, 40, 33, 65, 100, 300, 300]
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=260)
+    used = torch.zeros(260, dtype=torch.bool)
+    for t in tables:
+        used[t] = True
+    kc[~used.to(DEV)] = float("nan")
+    vc[~used.to(DEV)] = float("nan")
+    for t, kv in zip(tables, lens_kv):                 # the unwritten tail of each last page too
+        if kv % ps:
+            vc[t[-1], :, kv % ps:] = float("nan")
+            kc[t[-1], :, kv % ps:] = float("nan")
+    g = nq // nkv
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    work = torch.tensor([(e, t) for e, ql in enumerate(lens_q) for t in range((ql * g + 127) // 128)],
+                        dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_rows_tma(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, scale, window)
+    assert ops().gemm_error_flag(q.device) == 0
+    kc, vc = torch.nan_to_num(kc), torch.nan_to_num(vc)
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
