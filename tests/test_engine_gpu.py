@@ -175,3 +175,28 @@ def test_recorded_decode_steps_equal_eager_ones(folder_b):
         ref = plain_logits(folder_b, toks)
         for p in range(len(prompts[r]), len(toks)):
             assert np.abs(recorded[(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()
+
+
+LAYER_SIZES = {   # one block at the layer sizes of the large configurations, small vocabulary
+    "8b": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288),
+    "14b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128, intermediate_size=17408),
+    "32b": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=25600),
+}
+
+
+@pytest.mark.parametrize("size", ["8b", "14b", "32b"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_block_at_large_layer_sizes(size, dtype, tmp_path_factory):
+    """Logits of a one-layer model with the real layer sizes: whole prompt, then decoded tokens, then a
+    second request beside it, against the plain implementation."""
+    from conftest import make_folder
+    cfg = dict(TINY["B"][0], num_hidden_layers=1, vocab_size=512, max_position_embeddings=512, **LAYER_SIZES[size])
+    folder = make_folder(tmp_path_factory, cfg, 5, f"block_{size}")
+    eng = build(folder, dtype, num_pages=32, page_size=16)
+    rng = np.random.default_rng(1)
+    a, b = random_tokens(rng, 90, 512), random_tokens(rng, 21, 512)
+    steps = [{"entries": [("a", a[:70], list(range(70)))]},
+             {"entries": [("a", a[70:71], [0]), ("b", b[:20], list(range(20)))]}]
+    steps += [{"entries": [("a", a[71 + i:72 + i], [0])] + ([("b", b[20:], [0])] if i == 0 else [])} for i in range(19)]
+    got = replay(eng, steps)
+    check_against_plain(got, folder, {"a": a, "b": b}, dtype)

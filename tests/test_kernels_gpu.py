@@ -271,7 +271,8 @@ def test_argmax_ties_go_to_the_lowest_id():
 @pytest.mark.parametrize("M, N, K, splits", [
     (1, 128, 64, 1), (8, 384, 96, 1), (16, 192, 64, 1), (17, 200, 72, 1), (33, 4096, 4096, 4),
     (64, 2560, 4096, 1), (64, 512, 1024, 3), (100, 384, 256, 1), (129, 640, 512, 2), (300, 640, 520, 1),
-    (2048, 1024, 512, 1), (5, 6144, 4096, None), (8, 4096, 12288, None), (257, 128, 8, 1)])
+    (2048, 1024, 512, 1), (5, 6144, 4096, None), (8, 4096, 12288, None), (257, 128, 8, 1),
+    (40, 7168, 5120, None), (200, 5120, 17408, 1), (64, 10240, 5120, None), (520, 1280, 25600, 1)])
 @pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
 def test_gemm_tn_tcgen05(M, N, K, splits, odt):
     g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
@@ -425,7 +426,8 @@ def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
 
 
 @pytest.mark.parametrize("M, N, K", [(1, 16, 8), (1, 4096, 4096), (8, 6144, 4096), (8, 200, 72), (5, 17, 520),
-                                     (9, 384, 96), (16, 4096, 12288), (13, 1000, 264), (8, 151936, 512)])
+                                     (9, 384, 96), (16, 4096, 12288), (13, 1000, 264), (8, 151936, 512),
+                                     (8, 7168, 5120), (3, 5120, 25600)])
 @pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
 def test_gemm_tn_skinny(M, N, K, odt):
     g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
