@@ -19,10 +19,29 @@
 
 namespace srlm {
 
+// Optional fusions with the norms around a product (decode steps, M <= 8):
+//  * scale_parts: the tokens X are (residual * norm weight) in bfloat16, not yet divided by their RMS;
+//    the sums of squares of each token's residual row come in n_parts partial rows [n_parts][8] and the
+//    product is scaled by rsqrt(sum / norm_width + eps) per token.  Multiplying after the product is
+//    the same linear map, and the division happens in float32.
+//  * residual: instead of storing the product, add it to the float32 residual stream in place; and, if
+//    next_w is given, also emit for the norm that follows xw_out = bf16(residual * next_w) and this
+//    block's share of the row sums of squares, ss_out[blockIdx.x][token].
+struct SkinnyFuse {
+  const float* scale_parts;
+  int n_parts;
+  float inv_width, eps;
+  float* residual;
+  long long ldr;
+  const float* next_w;
+  bf16* xw_out;
+  long long ldxw;
+  float* ss_out;
+};
+
 constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_ROWS = 16;
-constexpr int SK_UNROLL = 4;
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {      // read once: do not keep in L1
   uint4 v;
@@ -41,11 +60,12 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, typename TO>     // MT token tiles of 8
+template <int MT, typename TO, int SK_UNROLL>     // MT token tiles of 8; SK_UNROLL groups of 32 k per batch
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ C, int M, int N, int K,
-                   long long ldx, long long ldw, long long ldc, int swiglu8) {
+                   long long ldx, long long ldw, long long ldc, int swiglu8, const SkinnyFuse fuse) {
   __shared__ float part[SK_WARPS][SK_ROWS][MT * 8 + 1];
+  __shared__ float row_scale[MT * 8];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, q = lane & 3;
@@ -85,6 +105,35 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
   };
   load_w(g_lo, a[0], b[0]);
   pdl_wait();
+  if (fuse.scale_parts) {
+    // 1 / RMS of each token's row from the partial sums of squares: every thread takes one partial
+    // row (8 tokens), warps add theirs with shuffles, warp sums meet in shared memory; the order of
+    // the additions is fixed by the thread layout, and the loads fly together with the weight loads
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = threadIdx.x; p < fuse.n_parts; p += SK_THREADS) {
+      const float4 lo = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8));
+      const float4 hi = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8 + 4));
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v[t] += __shfl_xor_sync(0xffffffffu, v[t], off);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) part[warp][0][t] = v[t];      // borrowed until the epilogue fills it
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+      float ss = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) ss += part[w][0][threadIdx.x];
+      row_scale[threadIdx.x] = rsqrtf(ss * fuse.inv_width + fuse.eps);
+    }
+    __syncthreads();
+  }
   int buf = 0;
   for (int g = g_lo; g < g_hi; g += SK_UNROLL, buf ^= 1) {
     uint4 x[SK_UNROLL][MT];
@@ -124,53 +173,108 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
         float gsum = 0.f, usum = 0.f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) { gsum += part[w][row][m]; usum += part[w][row + 8][m]; }
+        if (fuse.scale_parts) { gsum *= row_scale[m]; usum *= row_scale[m]; }
         const float sg = gsum >= 0.f ? gsum / (1.f + expf(-gsum)) : gsum * (expf(gsum) / (1.f + expf(gsum)));
         C[(size_t)m * ldc + (n0 >> 1) + row] = from_float<TO>(sg * usum);
       }
     }
     return;
   }
-  for (int idx = threadIdx.x; idx < SK_ROWS * MT * 8; idx += SK_THREADS) {
-    const int m = idx / SK_ROWS, row = idx % SK_ROWS;       // consecutive threads: consecutive n
-    if (m < M && n0 + row < N) {
-      float s = 0.f;
+  // idx = m * 16 + row: the 16 rows of a token sit in one half-warp (MT * 8 * 16 <= 256 threads)
+  {
+    const int idx = threadIdx.x;
+    const int m = idx / SK_ROWS, row = idx % SK_ROWS;
+    const bool live = idx < SK_ROWS * MT * 8 && m < M && n0 + row < N;
+    float s = 0.f;
+    if (live) {
 #pragma unroll
       for (int w = 0; w < SK_WARPS; ++w) s += part[w][row][m];
-      C[(size_t)m * ldc + n0 + row] = from_float<TO>(s);
+      if (fuse.scale_parts) s *= row_scale[m];
+    }
+    if (!fuse.residual) {
+      if (live) C[(size_t)m * ldc + n0 + row] = from_float<TO>(s);
+      return;
+    }
+    float r = 0.f;
+    if (live) {
+      float* res = fuse.residual + (size_t)m * fuse.ldr + n0 + row;
+      r = *res + s;
+      *res = r;
+      if (fuse.next_w) fuse.xw_out[(size_t)m * fuse.ldxw + n0 + row] = __float2bfloat16_rn(r * fuse.next_w[n0 + row]);
+    }
+    if (fuse.next_w && idx < SK_ROWS * MT * 8) {       // whole half-warps, so the shuffles below are complete
+      float sq = r * r;
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      if (row == 0 && m < 8) fuse.ss_out[(size_t)blockIdx.x * 8 + m] = sq;
     }
   }
 }
 
-template <int MT, typename TO>
-static int launch_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
-                         long long ldc, int swiglu8, cudaStream_t stream) {
+template <int MT, typename TO, int U>
+static int launch_skinny_u(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                           long long ldc, int swiglu8, const SkinnyFuse& fuse, cudaStream_t stream) {
   // A plain launch (full stream order): measured on B200, letting this kernel start under its
   // predecessor made whole decode steps slower, not faster.
-  gemm_skinny_kernel<MT, TO><<<dim3((N + SK_ROWS - 1) / SK_ROWS), dim3(SK_THREADS), 0, stream>>>(
-      (const bf16*)X, (const bf16*)W, (TO*)C, M, N, K, ldx, ldw, ldc, swiglu8);
+  gemm_skinny_kernel<MT, TO, U><<<dim3((N + SK_ROWS - 1) / SK_ROWS), dim3(SK_THREADS), 0, stream>>>(
+      (const bf16*)X, (const bf16*)W, (TO*)C, M, N, K, ldx, ldw, ldc, swiglu8, fuse);
   return launched();
+}
+
+template <int MT, typename TO>
+static int launch_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                         long long ldc, int swiglu8, const SkinnyFuse& fuse, cudaStream_t stream) {
+  // four groups of 32 k per batch: measured best of 2 / 4 / 6 on B200 (registers against loads in flight)
+  return launch_skinny_u<MT, TO, 4>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream);
 }
 
 }  // namespace srlm
 
 using namespace srlm;
 
-extern "C" int srlm_gemm_tn_skinny(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
-                                   long long ldx, long long ldw, long long ldc, int swiglu8, cudaStream_t stream) {
+static int skinny_entry(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K, long long ldx,
+                        long long ldw, long long ldc, int swiglu8, const SkinnyFuse& fuse, cudaStream_t stream) {
   if (M <= 0) return ST_OK;
   if (swiglu8 && (N % 16 || ldc < N / 2))
     return refuse(ST_BAD_SIZE, "gemm_skinny: the SwiGLU epilogue needs N=%d a multiple of 16 and ldc >= N/2", N);
   if (M > 16) return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d; this kernel takes at most 16 tokens", M);
-  if (N <= 0 || K <= 0 || ldx < K || ldw < K || (!swiglu8 && ldc < N))
+  if (N <= 0 || K <= 0 || ldx < K || ldw < K || (!swiglu8 && !fuse.residual && ldc < N))
     return refuse(ST_BAD_SIZE, "gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld", M, N, K, ldx, ldw, ldc);
   if (K % 8 || ldx % 8 || ldw % 8 || (((uintptr_t)X | (uintptr_t)W) & 15))
     return refuse(ST_BAD_ALIGN, "gemm_skinny: K and the leading dimensions must be multiples of 8 and the operands "
                   "16-byte aligned (16-byte loads)");
+  if ((fuse.scale_parts || fuse.residual) && M > 8)
+    return refuse(ST_BAD_SIZE, "gemm_skinny: the norm fusions take at most 8 tokens, got %d", M);
+  if (fuse.residual && swiglu8) return refuse(ST_BAD_SIZE, "gemm_skinny: residual and SwiGLU epilogues exclude each other");
+  if (fuse.residual && (fuse.ldr < N || (fuse.next_w && (!fuse.xw_out || !fuse.ss_out || fuse.ldxw < N))))
+    return refuse(ST_BAD_SIZE, "gemm_skinny: residual epilogue with incomplete arguments");
   if (c_dtype == DT_BF16)
-    return M <= 8 ? launch_skinny<1, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream)
-                  : launch_skinny<2, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream);
+    return M <= 8 ? launch_skinny<1, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream)
+                  : launch_skinny<2, bf16>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream);
   if (c_dtype == DT_F32)
-    return M <= 8 ? launch_skinny<1, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream)
-                  : launch_skinny<2, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, stream);
+    return M <= 8 ? launch_skinny<1, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream)
+                  : launch_skinny<2, float>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream);
   return refuse(ST_BAD_DTYPE, "gemm_skinny: output dtype %d", c_dtype);
+}
+
+extern "C" int srlm_gemm_tn_skinny(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                   long long ldx, long long ldw, long long ldc, int swiglu8, cudaStream_t stream) {
+  const SkinnyFuse none{};
+  return skinny_entry(X, W, C, c_dtype, M, N, K, ldx, ldw, ldc, swiglu8, none, stream);
+}
+
+// The same product fused with the norms around it (see SkinnyFuse).  scale_parts may be null (X is already
+// normalised); residual may be null (the product is stored to C as usual, possibly through SwiGLU).
+extern "C" int srlm_gemm_tn_skinny_fused(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                         long long ldx, long long ldw, long long ldc, int swiglu8,
+                                         const float* scale_parts, int n_parts, int norm_width, float eps,
+                                         float* residual, long long ldr, const float* next_w, void* xw_out,
+                                         long long ldxw, float* ss_out, cudaStream_t stream) {
+  if (scale_parts && (n_parts <= 0 || norm_width <= 0 || !(eps > 0.f)))
+    return refuse(ST_BAD_SIZE, "gemm_skinny_fused: n_parts=%d norm_width=%d eps=%g", n_parts, norm_width, (double)eps);
+  const SkinnyFuse fuse{scale_parts, n_parts, norm_width > 0 ? 1.f / (float)norm_width : 0.f, eps, residual, ldr,
+                        next_w, (bf16*)xw_out, ldxw, ss_out};
+  return skinny_entry(X, W, C, c_dtype, M, N, K, ldx, ldw, ldc, swiglu8, fuse, stream);
 }

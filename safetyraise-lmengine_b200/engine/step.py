@@ -216,7 +216,7 @@ class Engine:
             kv_slot={g.name: d("kv_slot:" + g.name) for g in groups},
             host={"q_lens": q_lens, "starts": starts, "kv_lens": kv_lens, "slots": [e.slot for e in entries]},
             cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens), kv_bound=pages * ps)
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens), kv_bound=pages * ps, options=self.mctx.options)
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         """Runs the model on the batch: eagerly, or by replaying the CUDA graph of this kind of step."""

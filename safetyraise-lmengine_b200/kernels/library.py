@@ -215,6 +215,37 @@ class KernelLibrary:
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)),
             C.c_int(int(swiglu8)), _stream()), "gemm_tn_skinny")
 
+    def gemm_tn_skinny_fused(self, a, w, out=None, swiglu8=False, scale_parts=None, norm_width=0, eps=0.0,
+                             residual=None, next_w=None, xw_out=None, ss_out=None):
+        """The weight-streaming product (at most 8 tokens) fused with the norms around it.
+
+        scale_parts [parts, 8] float32: ``a`` holds bf16(residual * norm weight); the product is scaled per
+        token by rsqrt(sum of the parts / norm_width + eps).  residual [M, N] float32: the product is added
+        to it in place instead of being stored; with next_w [N] also xw_out[M, N] = bf16(residual * next_w)
+        and ss_out [N/16, 8] (each block's share of the rows' sums of squares) are written."""
+        M, K = a.shape
+        N = w.shape[0]
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or M > 8:
+            raise ShapeError(f"gemm_skinny_fused: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+        if residual is None and (out is None or tuple(out.shape) != (M, N // 2 if swiglu8 else N)):
+            raise ShapeError("gemm_skinny_fused: out has the wrong shape")
+        if ss_out is not None and (ss_out.shape[0] < (N + 15) // 16 or ss_out.shape[1] != 8):
+            raise ShapeError("gemm_skinny_fused: ss_out must be [ceil(N/16), 8]")
+        self._check(self.lib.srlm_gemm_tn_skinny_fused(
+            _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype) if out is not None else DT_BF16, C.c_int(M),
+            C.c_int(N), C.c_int(K), C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)),
+            C.c_longlong(out.stride(0) if out is not None else N), C.c_int(int(swiglu8)), _ptr(scale_parts),
+            C.c_int(scale_parts.shape[0] if scale_parts is not None else 0), C.c_int(norm_width), C.c_float(eps),
+            _ptr(residual), C.c_longlong(residual.stride(0) if residual is not None else 0), _ptr(next_w),
+            _ptr(xw_out), C.c_longlong(xw_out.stride(0) if xw_out is not None else 0), _ptr(ss_out), _stream()),
+            "gemm_tn_skinny_fused")
+
+    def can_fuse_norms(self, T: int, dtype, w) -> bool:
+        """Whether a product of T tokens with this weight may take the norm fusions of the skinny kernel."""
+        return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= min(8, self.skinny_max_tokens)
+                and w.shape[1] % 8 == 0 and w.shape[0] <= self.skinny_max_rows
+                and not (self.force_simt_gemm or self.force_tcgen05_gemm))
+
     def can_fuse_swiglu(self, a_dtype, w) -> bool:
         """Whether gemm(..., swiglu8=True) is offered for these operands (the tensor-core kernels only)."""
         return (a_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0

@@ -57,10 +57,24 @@ class PagedAttention(Part):
         s = self.spec
         return CacheNeed(PAGED_WINDOW if s.window else PAGED_ALL, s.kv_heads, s.head_dim, s.window)
 
+    def can_fuse(self, ctx) -> bool:
+        return self.qkv.can_fuse(ctx, ctx.T) and self.out.can_fuse(ctx, ctx.T)
+
+    def forward_fused(self, ctx, nx, run_step: RunStep, residual: torch.Tensor, next_norm):
+        """The same as forward for a lazily normalised input, with the output projection adding into the
+        residual stream and preparing the input of the part behind ``next_norm``."""
+        qkv = ctx.workspace.get("attn.qkv", ctx.T, self.qkv.out_features, ctx.dtype)
+        self.qkv.from_normed(ctx, nx, qkv)
+        attended = self._attend(ctx, qkv, run_step)
+        return self.out.into_residual(ctx, attended, residual, next_norm, "a")
+
     def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
-        s = self.spec
-        T = x.shape[0]
         qkv = self.qkv(ctx, x, "attn.qkv")
+        return self.out(ctx, self._attend(ctx, qkv, run_step), "attn.proj")
+
+    def _attend(self, ctx, qkv: torch.Tensor, run_step: RunStep) -> torch.Tensor:
+        s = self.spec
+        T = qkv.shape[0]
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
         q = ctx.workspace.get("attn.q", T, s.heads * s.head_dim, ctx.dtype)
         if self.position is not None:
@@ -75,4 +89,4 @@ class PagedAttention(Part):
         attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
         ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
                             s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0)
-        return self.out(ctx, attended, "attn.proj")
+        return attended

@@ -122,6 +122,24 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     kv_bound: int = 1                         # an upper bound of max_kv_len that kernels may size their grids by
+    options: dict = field(default_factory=dict)   # the engine's options, for parts that have switches
+
+
+@dataclass
+class NormedInput:
+    """An activation on its way into a part, normalised lazily.
+
+    ``xw`` holds residual * norm weight in the activation dtype.  If ``ss_parts`` is None it is already
+    divided by its RMS (a plain normalised tensor).  Otherwise ``ss_parts`` [parts, 8] holds partial sums
+    of squares of each token's residual row, and whoever consumes ``xw`` with a linear map scales the
+    map's output by rsqrt(sum / width + eps) per token instead.  Produced by the epilogue of the product
+    that wrote the residual, consumed by the first product of the next part: the norm kernel between
+    the two disappears.
+    """
+    xw: torch.Tensor
+    ss_parts: Optional[torch.Tensor]
+    width: int
+    eps: float
 
 
 class Part:

@@ -40,8 +40,30 @@ class PreNormBlock(Part):
                 + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(
                     spec.feed_forward, p))
 
-    def forward(self, ctx, residual, pending, run_step: RunStep):
+    def fuses(self, ctx) -> bool:
+        """Whether this block runs its norms inside the products around them for this step: both parts
+        offer forward_fused and the step is small enough for the kernels that carry the fusions."""
+        return (getattr(self.mixer_norm, "fusable", False) and getattr(self.ff_norm, "fusable", False)
+                and hasattr(self.mixer, "forward_fused") and hasattr(self.feed_forward, "forward_fused")
+                and self.mixer.can_fuse(ctx) and self.feed_forward.can_fuse(ctx)
+                and not ctx.options.get("unfused_norms", False))
+
+    def forward(self, ctx, residual, pending, run_step: RunStep, next_norm=None):
+        """pending: what the block before left to be added (a tensor), or the already prepared input of
+        this block's first norm (a NormedInput), or None.  next_norm: the norm that will read the
+        residual after this block, if its block fuses too; then a NormedInput for it is returned."""
+        from .base import NormedInput
         T = residual.shape[0]
+        if self.fuses(ctx):
+            if isinstance(pending, NormedInput):
+                nx = pending
+            else:
+                n = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype)
+                self.mixer_norm.apply(residual, pending, n)
+                nx = NormedInput(n, None, self.hidden, self.mixer_norm.spec.eps)
+            nx = self.mixer.forward_fused(ctx, nx, run_step, residual, self.ff_norm)
+            return self.feed_forward.forward_fused(ctx, nx, residual, next_norm)
+        assert not isinstance(pending, NormedInput), "a fused block was promised to its predecessor"
         n = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype)
         self.mixer_norm.apply(residual, pending, n)
         mixed = self.mixer.forward(ctx, n, run_step)

@@ -43,6 +43,16 @@ class GatedDense(Part):
                 TensorDecl(p + "up_proj.weight", (spec.intermediate_size, spec.hidden_size), MATRIX),
                 TensorDecl(p + "down_proj.weight", (spec.hidden_size, spec.intermediate_size), MATRIX)]
 
+    def can_fuse(self, ctx) -> bool:
+        return self.fused and self.gate_up.can_fuse(ctx, ctx.T) and self.down.can_fuse(ctx, ctx.T)
+
+    def forward_fused(self, ctx, nx, residual: torch.Tensor, next_norm):
+        """forward for a lazily normalised input; the down projection adds into the residual stream and
+        prepares the input of the part behind ``next_norm`` (None: nothing follows)."""
+        h = ctx.workspace.get("ffn.h", ctx.T, self.spec.intermediate_size, ctx.dtype)
+        self.gate_up.from_normed(ctx, nx, h, swiglu8=True)
+        return self.down.into_residual(ctx, h, residual, next_norm, "f")
+
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         h = ctx.workspace.get("ffn.h", x.shape[0], self.spec.intermediate_size, ctx.dtype)
         if self.fused and ops.can_fuse_swiglu(x.dtype, self.gate_up.weight):

@@ -35,3 +35,28 @@ class Linear:
                 ops.cast(y32, out)
             return
         ops.gemm(x, w, out)
+
+    # ---- fused with the norms around it (decode steps of a few tokens) -------------------------
+    def can_fuse(self, ctx, T: int) -> bool:
+        return ops.can_fuse_norms(T, ctx.dtype, self.weight)
+
+    def from_normed(self, ctx, nx, out: torch.Tensor, swiglu8: bool = False) -> None:
+        """out = norm(x) . W^T for a lazily normalised input (see parts.base.NormedInput)."""
+        if nx.ss_parts is None:
+            ops.gemm(nx.xw, self.weight, out, swiglu8=swiglu8)
+        else:
+            ops.gemm_tn_skinny_fused(nx.xw, self.weight, out, swiglu8=swiglu8, scale_parts=nx.ss_parts,
+                                     norm_width=nx.width, eps=nx.eps)
+
+    def into_residual(self, ctx, x: torch.Tensor, residual: torch.Tensor, next_norm, slot: str):
+        """residual += x . W^T in the product's epilogue.  With ``next_norm`` (an RMSNorm part) the same
+        epilogue prepares the input of the part behind that norm and returns it as a NormedInput."""
+        from .base import NormedInput
+        if next_norm is None:
+            ops.gemm_tn_skinny_fused(x, self.weight, residual=residual)
+            return None
+        T, N = x.shape[0], self.out_features
+        xw = ctx.workspace.get("fused.xw." + slot, T, N, ctx.dtype)
+        ss = ctx.workspace.get("fused.ss." + slot, (N + 15) // 16, 8, torch.float32, reserve=0)
+        ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw, ss_out=ss)
+        return NormedInput(xw, ss, next_norm.spec.size, next_norm.spec.eps)

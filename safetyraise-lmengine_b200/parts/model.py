@@ -75,8 +75,18 @@ class DecoderModel:
         residual = ctx.workspace.get("residual", ctx.T, H, torch.float32)
         ops.embed_gather(ctx.token_ids, self.embed, residual, self.bad_flag)
         pending = None
-        for step in self.spec.run_order:
-            pending = self.blocks[step.layer].forward(ctx, residual, pending, step)
+        order = self.spec.run_order
+        for i, step in enumerate(order):
+            block = self.blocks[step.layer]
+            # a block may hand the next one its input already multiplied by that block's norm weight,
+            # if both run their norms inside the products (decode steps of a few tokens)
+            nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            next_norm = None
+            if nxt is not None and hasattr(block, "fuses") and hasattr(nxt, "fuses") and block.fuses(ctx) \
+                    and nxt.fuses(ctx):
+                next_norm = nxt.mixer_norm
+            pending = block.forward(ctx, residual, pending, step, next_norm) if hasattr(block, "fuses") \
+                else block.forward(ctx, residual, pending, step)
         R = ctx.logit_rows.shape[0]
         logits = ctx.workspace.get("logits", R, self.spec.vocab_size, torch.float32, reserve=64)
         if R == 0:          # nothing wanted: the step only had to fill the cache

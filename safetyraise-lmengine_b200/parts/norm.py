@@ -22,6 +22,11 @@ class RMSNorm(Part):
     def tensor_decls(cls, spec: NormSpec, name: str) -> List[TensorDecl]:
         return [TensorDecl(name, (spec.size,), VECTOR)]
 
+    @property
+    def fusable(self) -> bool:
+        """Whether products may apply this norm in their own prologue and epilogue (parts.base.NormedInput)."""
+        return not self.spec.unit_offset
+
     def apply(self, residual, delta, out, rows=None):
         """residual[float32] += delta (kept when rows is None); out = norm of the sum.
         With ``rows`` only those rows are normed, into out[0..len(rows))."""

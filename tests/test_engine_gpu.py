@@ -200,3 +200,28 @@ def test_one_block_at_large_layer_sizes(size, dtype, tmp_path_factory):
     steps += [{"entries": [("a", a[71 + i:72 + i], [0])] + ([("b", b[20:], [0])] if i == 0 else [])} for i in range(19)]
     got = replay(eng, steps)
     check_against_plain(got, folder, {"a": a, "b": b}, dtype)
+
+
+def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
+    """Decode steps of up to 8 tokens run their RMSNorms inside the products around them; the same
+    steps with the fusion switched off must give the same logits within rounding."""
+    cfg, _ = TINY["B"]
+    rng = np.random.default_rng(13)
+    reqs = {r: random_tokens(rng, n, cfg["vocab_size"]) for r, n in (("a", 30), ("b", 47), ("c", 12))}
+    steps = [{"entries": [(r, t[:-8], []) for r, t in reqs.items()]}]
+    steps += [{"entries": [(r, t[len(t) - 8 + i:len(t) - 7 + i], [0]) for r, t in reqs.items()]} for i in range(8)]
+    steps[-1]["end"] = list(reqs)
+    steps += [{"entries": [("d", reqs["a"][:5], [0, 4]), ("e", reqs["b"][:3], [2])]}]      # 8 prompt tokens
+    out = {}
+    for fused in (True, False):
+        eng = build(folder_b, "bfloat16", options={"unfused_norms": not fused, "cuda_graphs": False})
+        out[fused] = replay(eng, steps)
+    assert out[True].keys() == out[False].keys() and len(out[True]) == 3 * 8 + 3
+    for k in out[True]:
+        scale = np.abs(out[False][k]).max()
+        assert np.abs(out[True][k] - out[False][k]).max() <= 2e-2 * scale, k
+    full = {r: t for r, t in reqs.items()}
+    for r, t in full.items():
+        ref = plain_logits(folder_b, t)
+        for p in range(len(t) - 8, len(t)):
+            assert np.abs(out[True][(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()

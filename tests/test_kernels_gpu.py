@@ -510,3 +510,35 @@ def test_paged_attention_rows_tma(nq, nkv, hd, ps, window):
     kc, vc = torch.nan_to_num(kc), torch.nan_to_num(vc)
     ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
     assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 4096, 4096), (5, 200, 520), (8, 96, 264)])
+def test_gemm_skinny_with_fused_norms(M, N, K):
+    """residual += x.W^T with the next norm prepared in the epilogue, then a product that consumes it."""
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    residual = torch.randn(M, N, device=DEV, generator=g) * 2
+    nw = 1 + 0.1 * torch.randn(N, device=DEV, generator=g)
+    eps = 1e-5
+    res = residual.clone()
+    xw = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ss = torch.full(((N + 15) // 16, 8), float("nan"), device=DEV)
+    ops().gemm_tn_skinny_fused(x, w1, residual=res, next_w=nw, xw_out=xw, ss_out=ss)
+    new_res = residual.double() + x.double() @ w1.double().T
+    assert torch.allclose(res.double(), new_res, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(xw.double(), new_res * nw.double(), rtol=1e-2, atol=1e-2)
+    assert torch.allclose(ss.sum(0)[:M].double(), (new_res ** 2).sum(-1), rtol=1e-4)
+    assert torch.all(ss[:, M:] == 0)
+    # the consumer: y = rmsnorm(new_res) . W2^T through the lazily normalised input
+    N2 = 48
+    w2 = (torch.randn(N2, N, device=DEV, generator=g) / math.sqrt(N)).to(torch.bfloat16) if N % 8 == 0 else None
+    if w2 is not None:
+        y = torch.full((M, N2), float("nan"), device=DEV, dtype=torch.float32)
+        ops().gemm_tn_skinny_fused(xw, w2, y, scale_parts=ss, norm_width=N, eps=eps)
+        normed = new_res * torch.rsqrt((new_res ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+        assert torch.allclose(y.double(), normed @ w2.double().T, rtol=2e-2, atol=2e-2)
+    # residual only (nothing follows)
+    res2 = residual.clone()
+    ops().gemm_tn_skinny_fused(x, w1, residual=res2)
+    assert torch.equal(res2, res)
