@@ -334,18 +334,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int rows = min(BN, args.M - m0), nz = (int)gridDim.z;
         const size_t slab = (size_t)args.M * args.N;
         const bool have = n < args.N;
-        for (int j = 0; j < rows; j += 4) {
-          // four rows at a time: the loads of a row do not wait for the sums of the one before
-          float x[4] = {0.f, 0.f, 0.f, 0.f};
+        // 64 rows per round: each round is one trip to L2 with 64 loads in flight per thread, and
+        // there are as many rounds as splits (the sum order stays: split 0, 1, 2, ...)
+        constexpr int RB = 64;
+        for (int j = 0; j < rows; j += RB) {
+          float x[RB];
+#pragma unroll
+          for (int u = 0; u < RB; ++u) x[u] = 0.f;
           if (have) {
             for (int z = 0; z < nz; ++z) {
 #pragma unroll
-              for (int u = 0; u < 4; ++u)
+              for (int u = 0; u < RB; ++u)
                 if (j + u < rows) x[u] += __ldcg(&args.partial[z * slab + (size_t)(m0 + j + u) * args.N + n]);
             }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < RB; ++u)
             if (j + u < rows) store_result(args, m0 + j + u, n, x[u], have);
         }
       }

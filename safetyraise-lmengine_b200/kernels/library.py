@@ -173,6 +173,10 @@ class KernelLibrary:
         total_kb = (K + 63) // 64
         if tiles >= 1024 or M > 256:
             return 1
+        if M > 16:
+            # measured on B200: beyond 16 tokens the partial sums cost more than the idle SMs, except
+            # for a long K with few tiles (the down projection at 17..32 tokens)
+            return 4 if (M <= 32 and total_kb >= 128 and tiles < 64) else 1
         best, best_eff = 1, 0.0
         for s in range(1, 17):
             if s > 1 and (total_kb // s < 4 or 65536 + s * M * N * 4 > KernelLibrary.GEMM_WS_BYTES):
