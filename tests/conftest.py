@@ -29,7 +29,21 @@ TINY_B = {
     "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 256,
     "eos_token_id": [7, 9],
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# Two more with awkward sizes: C has a head size that is no multiple of 64 and as many KV heads as
+# query heads; D has a width that is no multiple of 8 (no TMA, no 16-byte rows), 3 query heads per KV head.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 120, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 200, "vocab_size": 333, "rope_theta": 50000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 192,
+}
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 80, "intermediate_size": 132, "vocab_size": 257, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 192,
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def make_folder(tmp_path_factory_or_dir, config, seed, name="model"):
@@ -49,7 +63,7 @@ def folder_b(tmp_path_factory):
     return make_folder(tmp_path_factory, TINY_B, 1, "tiny_b")
 
 
-@pytest.fixture(scope="session", params=["A", "B"])
+@pytest.fixture(scope="session", params=["A", "B", "C", "D"])
 def tiny_folder(request, tmp_path_factory):
     cfg, seed = TINY[request.param]
     return request.param, make_folder(tmp_path_factory, cfg, seed, "tiny_" + request.param.lower())

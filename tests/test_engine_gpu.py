@@ -20,7 +20,7 @@ def build(folder, dtype, num_pages=64, page_size=16, **kw):
 def requests_for(name, seed=0):
     cfg, _ = TINY[name]
     rng = np.random.default_rng(100 + seed)
-    lens = [5, 11, 17, 70] if name == "A" else [1, 7, 33, 64, 100]
+    lens = [5, 11, 17, 70] if name in ("A", "C") else [1, 7, 33, 64, 100]
     return {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
 
 
