@@ -51,6 +51,7 @@ class KernelLibrary:
         self.skinny_max_tokens = int(os.environ.get("SRLM_SKINNY_TOKENS", "8"))
         self.skinny_max_rows = int(os.environ.get("SRLM_SKINNY_ROWS", str(1 << 30)))
         self.force_cp_async_decode = False
+        self.force_mma_sync_prefill = False
 
     @property
     def lib(self):
@@ -66,6 +67,12 @@ class KernelLibrary:
             if os.environ.get("SRLM_PDL", "1") == "0":     # plain stream order between kernels
                 self._lib.srlm_set_pdl(0)
         return self._lib
+
+    def sm_count(self, device) -> int:
+        counts = self.__dict__.setdefault("_sm_counts", {})
+        if device not in counts:
+            counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+        return counts[device]
 
     def set_pdl(self, on: bool) -> None:
         """Programmatic dependent launch between the kernels of a step (on by default)."""
@@ -289,6 +296,18 @@ class KernelLibrary:
             C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
             _ptr(err), _stream()), "paged_attention_rows_tma")
 
+    def paged_attention_prefill_tcgen05(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv,
+                                        hd, page_size, scale, window=0, tiles_per_block=2):
+        """Rows-split attention on tcgen05 tensor cores with accumulators in tensor memory (head size
+        128; page_size 8..64 a power of two, or a multiple of 128); work: int32 [n, 2] (entry, block of
+        tiles_per_block x 128 rows), tiles_per_block 1 or 2."""
+        err = self._gemm_state(q.device)[1]
+        self._check(self.lib.srlm_paged_attention_prefill_tcgen05(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+            C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
+            C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+            C.c_int(tiles_per_block), _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
+
     def paged_attention_keys(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv, hd,
                              page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
         """bfloat16 tensor-core attention when every entry has at most 16 rows (decode); keys in nsplit slices."""
@@ -367,24 +386,36 @@ class KernelLibrary:
             self.paged_attention_keys(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries,
                                       nq, nkv, hd, page_size, scale, window, chunk, nsplit, part_o, part_ml)
             return
+        def work_list(rows_per_block):
+            work = ctx.tables.get(("attention_rows_work", g, rows_per_block))
+            if work is None:
+                # the last row blocks of an entry see the most keys: they go first, so that the long
+                # blocks do not start when the short ones have already left the GPU half empty
+                pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"])
+                         for t in reversed(range((ql * g + rows_per_block - 1) // rows_per_block))]
+                pairs.sort(key=lambda et: -(ctx.host["starts"][et[0]] + (et[1] + 1) * rows_per_block // g))
+                work = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(q.device, non_blocking=True)
+                ctx.tables[("attention_rows_work", g, rows_per_block)] = work
+            return work
+
+        if (self.lib.srlm_attention_prefill_tcgen05_takes(C.c_int(hd), C.c_int(page_size))
+                and not self.force_mma_sync_prefill):
+            # two row tiles per block share the key tiles and keep the tensor core busy while one of
+            # them is in its softmax; one row tile per block when two would leave SMs without a block
+            pairs_of_tiles = sum((ql * g + 255) // 256 for ql in ctx.host["q_lens"]) * nkv
+            tiles = 2 if pairs_of_tiles >= self.sm_count(q.device) else 1
+            self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
+                                                 work_list(128 * tiles), nq, nkv, hd, page_size, scale, window,
+                                                 tiles)
+            return
         tma = (hd in (64, 128) and self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))
                and not self.force_cp_async_decode)
-        rows_per_tile = 128 if tma else 64
-        work = ctx.tables.get(("attention_rows_work", g, rows_per_tile))
-        if work is None:
-            # the last row tiles of an entry see the most keys: they go first, so that the long blocks
-            # do not start when the short ones have already left the GPU half empty
-            pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"])
-                     for t in reversed(range((ql * g + rows_per_tile - 1) // rows_per_tile))]
-            pairs.sort(key=lambda et: -(ctx.host["starts"][et[0]] + (et[1] + 1) * rows_per_tile // g))
-            work = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(q.device, non_blocking=True)
-            ctx.tables[("attention_rows_work", g, rows_per_tile)] = work
         if tma:
-            self.paged_attention_rows_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq,
-                                          nkv, hd, page_size, scale, window)
+            self.paged_attention_rows_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
+                                          work_list(128), nq, nkv, hd, page_size, scale, window)
         else:
-            self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work, nq, nkv,
-                                      hd, page_size, scale, window)
+            self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work_list(64),
+                                      nq, nkv, hd, page_size, scale, window)
 
     # ---- sampling -------------------------------------------------------------
     def argmax(self, logits, out_tokens, bad_flag):

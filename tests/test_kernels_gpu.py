@@ -512,6 +512,58 @@ def test_paged_attention_rows_tma(nq, nkv, hd, ps, window):
     assert torch.allclose(out.float().cpu().view(-1, nq, hd).double(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nq, nkv, ps", [(32, 8, 16), (8, 2, 8), (4, 4, 32), (16, 1, 64), (6, 2, 128), (5, 5, 16)])
+@pytest.mark.parametrize("window", [0, 37, 200])
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_paged_attention_prefill_tcgen05(nq, nkv, ps, window, tiles):
+    """The tcgen05 prefill attention: ragged entries, partly filled pages, pages of other requests and
+    unwritten page tails poisoned with NaN, a far key that must win the softmax."""
+    hd = 128
+    lens_q, lens_kv = [1, 7, 33, 1, 2, 150, 300, 520], [1, 40, 33, 65, 100, 300, 300, 700]
+    pages = 120 + sum(-(-kv // ps) for kv in lens_kv)
+    q, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=pages)
+    used = torch.zeros(pages, dtype=torch.bool)
+    for t in tables:
+        used[t] = True
+    kc[~used.to(DEV)] = float("nan")
+    vc[~used.to(DEV)] = float("nan")
+    for t, kv in zip(tables, lens_kv):
+        if kv % ps:
+            vc[t[-1], :, kv % ps:] = float("nan")
+            kc[t[-1], :, kv % ps:] = float("nan")
+    if window == 0:
+        # the last entry's last row looks hard at key 3 (a far key among hundreds)
+        kc[tables[-1][3 // ps], :, 3 % ps] = 0
+        kc[tables[-1][3 // ps], :, 3 % ps, 0] = 30.0
+        q.view(-1, nq, hd)[-1] = 0
+        q.view(-1, nq, hd)[-1, :, 0] = 30.0
+    g = nq // nkv
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    rows = 128 * tiles
+    work = torch.tensor([(e, t) for e, ql in enumerate(lens_q) for t in reversed(range((ql * g + rows - 1) // rows))],
+                        dtype=torch.int32, device=DEV)
+    out = torch.full_like(q, float("nan"))
+    scale = 1 / math.sqrt(hd)
+    ops().paged_attention_prefill_tcgen05(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, scale, window, tiles)
+    torch.cuda.synchronize()
+    assert ops().gemm_error_flag(q.device) == 0
+    kc, vc = torch.nan_to_num(kc), torch.nan_to_num(vc)
+    ref = ref_paged_attention(q, kc, vc, tables, eot.cpu(), pos.cpu(), nq, nkv, hd, ps, scale, window)
+    got = out.float().cpu().view(-1, nq, hd).double()
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, ref, rtol=2e-2, atol=2e-2)
+
+
+def test_paged_attention_prefill_tcgen05_refuses():
+    q = torch.zeros(4, 2, 64, device=DEV, dtype=torch.bfloat16)
+    kc = torch.zeros(4, 2, 16, 64, device=DEV, dtype=torch.bfloat16)
+    bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(Exception, match="attention_prefill_tcgen05"):
+        ops().paged_attention_prefill_tcgen05(q, kc, kc, q.clone(), bt, z, z, z.view(1, 2), 2, 2, 64, 16, 1.0, 0)
+
+
 @pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 4096, 4096), (5, 200, 520), (8, 96, 264)])
 def test_gemm_skinny_with_fused_norms(M, N, K):
     """residual += x.W^T with the next norm prepared in the epilogue, then a product that consumes it."""
