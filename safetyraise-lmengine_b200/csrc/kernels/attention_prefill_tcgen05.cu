@@ -154,6 +154,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -178,44 +185,43 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int row, int c16) {
 }
 
 
-// The maximum of the keys [k_lo, k_hi) of one row of S (all 128 keys when not MASKED).
+// One row of S (128 keys) in registers: the four loads are in flight together.
+struct Row {
+  uint32_t a[32], b[32], c[32], d[32];
+};
+__device__ __forceinline__ void load_row(uint32_t s_addr, Row& r) {
+  tmem_ld32(s_addr, r.a);
+  tmem_ld32(s_addr + 32, r.b);
+  tmem_ld32(s_addr + 64, r.c);
+  tmem_ld32(s_addr + 96, r.d);
+  tmem_wait_ld();
+}
+// The maximum of the keys [k_lo, k_hi) of the row (all 128 keys when not MASKED).
 template <bool MASKED>
-__device__ __forceinline__ float row_max(uint32_t s_addr, int k_lo, int k_hi) {
+__device__ __forceinline__ float row_max(const Row& r, int k_lo, int k_hi) {
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
-  uint32_t va[32], vb[32];
-  tmem_ld32(s_addr, va);
-#pragma unroll
-  for (int c = 0; c < KT; c += 64) {
-    tmem_wait_ld();
-    tmem_ld32(s_addr + c + 32, vb);
+  auto part = [&](const uint32_t (&v)[32], int c) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-      if (!MASKED || (c + j >= k_lo && c + j < k_hi)) m0 = fmaxf(m0, __uint_as_float(va[j]));
-      if (!MASKED || (c + j + 1 >= k_lo && c + j + 1 < k_hi)) m1 = fmaxf(m1, __uint_as_float(va[j + 1]));
-      if (!MASKED || (c + j + 2 >= k_lo && c + j + 2 < k_hi)) m2 = fmaxf(m2, __uint_as_float(va[j + 2]));
-      if (!MASKED || (c + j + 3 >= k_lo && c + j + 3 < k_hi)) m3 = fmaxf(m3, __uint_as_float(va[j + 3]));
+      const int k = c + j;
+      if (!MASKED || (k >= k_lo && k < k_hi)) m0 = fmaxf(m0, __uint_as_float(v[j]));
+      if (!MASKED || (k + 1 >= k_lo && k + 1 < k_hi)) m1 = fmaxf(m1, __uint_as_float(v[j + 1]));
+      if (!MASKED || (k + 2 >= k_lo && k + 2 < k_hi)) m2 = fmaxf(m2, __uint_as_float(v[j + 2]));
+      if (!MASKED || (k + 3 >= k_lo && k + 3 < k_hi)) m3 = fmaxf(m3, __uint_as_float(v[j + 3]));
     }
-    tmem_wait_ld();
-    if (c + 64 < KT) tmem_ld32(s_addr + c + 64, va);
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const int k = c + 32 + j;
-      if (!MASKED || (k >= k_lo && k < k_hi)) m0 = fmaxf(m0, __uint_as_float(vb[j]));
-      if (!MASKED || (k + 1 >= k_lo && k + 1 < k_hi)) m1 = fmaxf(m1, __uint_as_float(vb[j + 1]));
-      if (!MASKED || (k + 2 >= k_lo && k + 2 < k_hi)) m2 = fmaxf(m2, __uint_as_float(vb[j + 2]));
-      if (!MASKED || (k + 3 >= k_lo && k + 3 < k_hi)) m3 = fmaxf(m3, __uint_as_float(vb[j + 3]));
-    }
-  }
+  };
+  part(r.a, 0);
+  part(r.b, 32);
+  part(r.c, 64);
+  part(r.d, 96);
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
-
 // P = exp2(S * scale - base) as bfloat16 pairs over the first 64 columns of S; returns the row sum.
 template <bool MASKED>
-__device__ __forceinline__ float row_exp(uint32_t s_addr, float scale, float base, int k_lo, int k_hi) {
+__device__ __forceinline__ float row_exp(uint32_t s_addr, const Row& r, float scale, float base, int k_lo, int k_hi) {
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   const float nb = -base;
-  uint32_t va[32], vb[32];
-  auto chunk = [&](const uint32_t (&v)[32], int c) {
+  auto part = [&](const uint32_t (&v)[32], int c) {
     uint32_t pk[16];
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
@@ -234,18 +240,12 @@ __device__ __forceinline__ float row_exp(uint32_t s_addr, float scale, float bas
       pk[j >> 1] = pack2(p0, p1);
       pk[(j >> 1) + 1] = pack2(p2, p3);
     }
-    tmem_st16(s_addr + (c >> 1), pk);       // behind the columns of S that are read: never ahead of a load
+    tmem_st16(s_addr + (c >> 1), pk);
   };
-  tmem_ld32(s_addr, va);
-#pragma unroll
-  for (int c = 0; c < KT; c += 64) {
-    tmem_wait_ld();
-    tmem_ld32(s_addr + c + 32, vb);
-    chunk(va, c);
-    tmem_wait_ld();
-    if (c + 64 < KT) tmem_ld32(s_addr + c + 64, va);
-    chunk(vb, c + 32);
-  }
+  part(r.a, 0);
+  part(r.b, 32);
+  part(r.c, 64);
+  part(r.d, 96);
   return (s0 + s1) + (s2 + s3);
 }
 
@@ -264,10 +264,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   uint64_t* s_full = v_empty + KV_STAGES;                // [2]: per row tile
   uint64_t* p_ready = s_full + 2;                        // [2]
   uint64_t* o_done = p_ready + 2;                        // [2]
-  uint64_t* v_clean = o_done + 2;                        // V rows without a key of the request are zeroed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_clean + 1);
+  uint64_t* v_clean = o_done + 2;                        // [2]: V rows without a key of the request are zeroed
+  uint64_t* q_full = v_clean + 2;                        // the Q tiles are written (every warp but the producer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 1);
 
-  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < KV_STAGES; ++s) {
@@ -281,7 +281,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       mbar_init(&p_ready[i], 4);
       mbar_init(&o_done[i], 1);
     }
-    mbar_init(v_clean, 1);
+    mbar_init(&v_clean[0], 1);
+    mbar_init(&v_clean[1], 1);
+    mbar_init(q_full, THREADS / 32 - 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
@@ -291,9 +293,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = *tmem_slot;
+  pdl_trigger();
   pdl_wait();
 
-  const int e = a.work[2 * blockIdx.x], bt = a.work[2 * blockIdx.x + 1], kvh = blockIdx.y;
+  // the grid runs over (block of rows, KV head) with the heads fastest: the work list is sorted by
+  // length, and blocks start in the order of their index
+  const int item = blockIdx.x / a.nkv, kvh = blockIdx.x % a.nkv;
+  const int e = a.work[2 * item], bt = a.work[2 * item + 1];
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
   const int rows_total = q_len * g;
@@ -313,23 +323,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   const bool dirty_first = a.window > 0 && jb0 < first_key;
   const bool dirty_last = jb0 + n_tiles1 * KT > kv_len;
 
-  // Q rows -> shared memory in the swizzled K-major layout (zeros beyond the entry's rows)
-  for (int idx = threadIdx.x; idx < (two ? 2 : 1) * BR * 16; idx += THREADS) {
-    const int row = idx >> 4, c = idx & 15;
-    const int r = r_block + row;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows_total)
-      v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + r / g) * a.nq + kvh * g + r % g) * HD + c * 8);
-    // a block of one row tile keeps it in slot 1
-    const uint32_t tile = s32(q_t) + ((two ? row >> 7 : 1) * TILE_BYTES);
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr(tile, row & 127, c)), "r"(v.x), "r"(v.y),
-                 "r"(v.z), "r"(v.w) : "memory");
+  if (warp != 0) {
+    // Q rows -> shared memory in the swizzled K-major layout (zeros beyond the entry's rows), while
+    // warp 0 already fetches the first keys
+    for (int idx = threadIdx.x - 32; idx < (two ? 2 : 1) * BR * 16; idx += THREADS - 32) {
+      const int row = idx >> 4, c = idx & 15;
+      const int r = r_block + row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_total)
+        v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + r / g) * a.nq + kvh * g + r % g) * HD + c * 8);
+      // a block of one row tile keeps it in slot 1
+      const uint32_t tile = s32(q_t) + ((two ? row >> 7 : 1) * TILE_BYTES);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr(tile, row & 127, c)), "r"(v.x), "r"(v.y),
+                   "r"(v.z), "r"(v.w) : "memory");
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(q_full);
   }
-  fence_async_smem();
-  fence_before();
-  __syncthreads();
-  fence_after();
-  const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
     // ---------------- TMA producer (lane 0 issues; the warp zeroes dirty V rows) ----------------
@@ -370,7 +381,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(v_clean);
+        if (lane == 0) mbar_arrive(&v_clean[df ? 0 : 1]);   // each is used once: a waiter cannot fall a phase behind
       }
     };
     for (int t = 0; t < n_tiles1 && ok; ++t) {
@@ -387,18 +398,22 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(KT, false), idesc_o = umma_idesc(HD, true);
       bool ok = true;
-      int cleaned = 0;
       auto wait_k = [&](int t) {
         ok = ok && mbar_wait(&k_full[t % KV_STAGES], (t / KV_STAGES) & 1, a.err_flag, 42);
         fence_after();
       };
+      // descriptors: the start address sits in the low bits, in units of 16 bytes, so a k-step is an addition
+      const uint64_t q_desc = umma_desc(s32(q_t), 0, 1024), k_desc = umma_desc(s32(k_t), 0, 1024);
+      const uint64_t v_desc = umma_desc(s32(v_t), KT * 128, 1024);
       auto issue_s = [&](int i, int t) {            // S_i = Q_i . K_t^T
         if (!ok) return;
-        const uint32_t qa = s32(q_t + i * TILE_BYTES), ka = s32(k_t + (t % KV_STAGES) * TILE_BYTES);
+        const uint64_t qd = q_desc + (uint64_t)(i * (TILE_BYTES >> 4));
+        const uint64_t kd = k_desc + (uint64_t)((t % KV_STAGES) * (TILE_BYTES >> 4));
+        const uint32_t d = tmem + i * 128;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;       // panel, then 32 bytes per k-step
-          umma_bf16(tmem + i * 128, umma_desc(qa + off, 0, 1024), umma_desc(ka + off, 0, 1024), idesc_s, ks != 0);
+          const uint32_t off = ((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4;   // panel, then 32 bytes per k-step
+          umma_bf16(d, qd + off, kd + off, idesc_s, ks != 0);
         }
         umma_commit(&s_full[i]);
       };
@@ -406,14 +421,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
         ok = ok && mbar_wait(&p_ready[i], t & 1, a.err_flag, 43);
         if (!ok) return;
         fence_after();
-        const uint32_t va = s32(v_t + (t % KV_STAGES) * TILE_BYTES);
+        const uint64_t vd = v_desc + (uint64_t)((t % KV_STAGES) * (TILE_BYTES >> 4));
+        const uint32_t d = tmem + 256 + i * 128, p = tmem + i * 128;
+        // A = P: 16 keys are 8 columns of bfloat16 pairs; B = V: MN-major, 16 keys are 2048 bytes
+        umma_bf16_ts(d, p, vd, idesc_o, t != 0);
 #pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk)
-          // A = P: 16 keys are 8 columns of bfloat16 pairs; B = V: MN-major, 16 keys are 2048 bytes
-          umma_bf16_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, umma_desc(va + kk * 2048, KT * 128, 1024),
-                       idesc_o, (t | kk) != 0);
+        for (int kk = 1; kk < KT / 16; ++kk) umma_bf16_ts(d, p + kk * 8, vd + kk * (2048 >> 4), idesc_o, 1);
         umma_commit(&o_done[i]);
       };
+      ok = mbar_wait(q_full, 0, a.err_flag, 51);
       wait_k(0);
       if (n_tiles0 > 0) issue_s(0, 0);
       issue_s(1, 0);
@@ -421,8 +437,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       for (int t = 0; t < n_tiles1 && ok; ++t) {
         const int s = t % KV_STAGES;
         ok = mbar_wait(&v_full[s], (t / KV_STAGES) & 1, a.err_flag, 48);
-        if (ok && ((dirty_first && t == 0) || (dirty_last && t == n_tiles1 - 1)))
-          ok = mbar_wait(v_clean, (cleaned++) & 1, a.err_flag, 50);
+        if (ok && dirty_first && t == 0)
+          ok = mbar_wait(&v_clean[0], 0, a.err_flag, 50);
+        else if (ok && dirty_last && t == n_tiles1 - 1)
+          ok = mbar_wait(&v_clean[1], 0, a.err_flag, 50);
         if (!ok) break;
         const bool more = t + 1 < n_tiles1;
         if (t < n_tiles0) issue_pv(0, t);
@@ -462,7 +480,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       fence_after();
       const bool full = jb >= lo_max && jb + KT - 1 <= pos_min;
       const int k_lo = max(0, lo - jb), k_hi = min(KT, pos - jb + 1);
-      const float mx = (full ? row_max<false>(s_addr, 0, KT) : row_max<true>(s_addr, k_lo, k_hi)) * a.scale_log2;
+      Row srow;
+      load_row(s_addr, srow);
+      const float mx = (full ? row_max<false>(srow, 0, KT) : row_max<true>(srow, k_lo, k_hi)) * a.scale_log2;
       // the reference of the exponentials moves only when the maximum has grown by more than 2^8
       const bool grow = mx > m_run + RESCALE_ABOVE || m_run == -CUDART_INF_F;
       const float m_new = grow ? fmaxf(mx, m_run) : m_run;
@@ -471,20 +491,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
         ok = mbar_wait(&o_done[i], (t - 1) & 1, a.err_flag, 45);          // P.V of the tile before is in O
         fence_after();
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(o_addr + c, v);
+        for (int c = 0; c < HD; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(o_addr + c, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(o_addr + c, v);
+          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st16(o_addr + c, v);
         }
         l_run *= alpha;
       }
       m_run = m_new;
       const float base = m_run == -CUDART_INF_F ? 0.f : m_run;
-      l_run += full ? row_exp<false>(s_addr, a.scale_log2, base, 0, KT)
-                    : row_exp<true>(s_addr, a.scale_log2, base, k_lo, k_hi);
+      l_run += full ? row_exp<false>(s_addr, srow, a.scale_log2, base, 0, KT)
+                    : row_exp<true>(s_addr, srow, a.scale_log2, base, k_lo, k_hi);
       tmem_wait_st();
       fence_before();
       __syncwarp();
@@ -605,6 +625,7 @@ extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k
   }
   fmha::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, page_size,
                tiles_per_block, scale * 1.4426950408889634f, window, err_flag};
-  launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work, nkv), dim3(fmha::THREADS), SMEM, stream, *mk, *mv, a);
+  launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work * nkv), dim3(fmha::THREADS), SMEM, stream, *mk, *mv, a);
   return launched();
 }
+
