@@ -131,7 +131,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   constexpr int PANELS = HD / 64;
   constexpr int TILE_BYTES = KT * HD * 2;            // one K or V tile
   constexpr int KS = HD / 16;                        // k steps of Q.K^T
-  constexpr int NT_O = HD / 8 / CONSUMERS;           // output n-tiles per consumer warp
+  constexpr int NT_ALL = HD / 8;                     // output n-tiles (every consumer warp holds all dims)
+  constexpr int KW = KT / CONSUMERS;                 // keys of a tile per consumer warp
+  constexpr int OS = HD + 8;                         // row stride of the merge buffer, in floats
+  static_assert(KW == 16, "a consumer warp takes one k-step of 16 keys per tile");
+  static_assert(CONSUMERS * 16 * (OS + 2) * 4 <= STAGES * 2 * TILE_BYTES, "the merge buffer lives in the tile memory");
   extern __shared__ uint8_t dec_smem_raw[];
   uint8_t* smem = dec_smem_raw + ((1024u - (s32(dec_smem_raw) & 1023u)) & 1023u);
   uint8_t* tiles = smem;                                              // [STAGES][K tile | V tile]
@@ -140,14 +144,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* empty_bar = full_bar + STAGES;
   __shared__ int is_last;
 
-  pdl_trigger();
   if (threadIdx.x == 0) {                 // nothing here depends on the kernel ahead
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CONSUMERS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
   }
+  __syncthreads();                        // the barriers are set up for every warp
   pdl_wait();
+  pdl_trigger();
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -160,53 +165,64 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int jb0 = max(slice_lo, (first_key / KT) * KT);
   const int n_tiles = slice_hi > jb0 ? (slice_hi - jb0 + KT - 1) / KT : 0;
 
-  // Q rows -> shared memory (plain loads: 16 rows at most)
-  for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
-    const int row = idx / (HD / 8), c = idx % (HD / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < rows_total)
-      v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + c * 8);
-    *reinterpret_cast<uint4*>(q_s + row * (HD + 8) + c * 8) = v;
+  // Q rows -> shared memory (plain loads: 16 rows at most), by the consumer warps; the producer warp
+  // is already fetching the first tiles
+  if (warp < CONSUMERS) {
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += CONSUMERS * 32) {
+      const int row = idx / (HD / 8), c = idx % (HD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < rows_total)
+        v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + c * 8);
+      *reinterpret_cast<uint4*>(q_s + row * (HD + 8) + c * 8) = v;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
   }
-  __syncthreads();
 
-  float o[NT_O][4];
+  float o[NT_ALL][4];
 #pragma unroll
-  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < NT_ALL; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
 
   if (warp == CONSUMERS) {
-    // ---------------- producer ----------------
-    if (lane == 0) {
-      const int ps = a.page_size;
-      const int box_rows = ps < KT ? ps : KT;          // keys per TMA copy
-      const int boxes = KT / box_rows;
-      uint64_t stream_once;                            // the cache is read once per step: first to leave L2
-      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_once));
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % STAGES, j = t / STAGES;
-        if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, a.err_flag, 11)) break;
-        mbar_expect_tx(&full_bar[s], 2 * TILE_BYTES);
-        uint8_t* kt = tiles + s * 2 * TILE_BYTES;
+    // ---------------- producer: lane b fetches page box b of every tile ----------------
+    // The page numbers come from the block table in global memory; with one lane per box the
+    // look-ups of a tile run side by side, and the next tile's are in flight during the wait.
+    const int ps = a.page_size;
+    const int box_rows = ps < KT ? ps : KT;          // keys per TMA copy
+    const int boxes = KT / box_rows;
+    uint64_t stream_once;                            // the cache is read once per step: first to leave L2
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_once));
+    auto box_row = [&](int t) {                      // row of the [pages * nkv * ps, HD] view, or -1
+      if (lane >= boxes || t >= n_tiles) return -1;
+      const int key = jb0 + t * KT + lane * box_rows;
+      const int pg = key / ps;
+      // beyond the request's pages (keys that no row sees): any valid page will do, they are masked
+      const int page = (pg < a.table_stride && key < kv_len) ? max(table[pg], 0) : 0;
+      return (page * a.nkv + kvh) * ps + key % ps;
+    };
+    int row_next = box_row(0);
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % STAGES, j = t / STAGES;
+      const int row = row_next;
+      row_next = box_row(t + 1);
+      if (!mbar_wait(&empty_bar[s], (j & 1) ^ 1, a.err_flag, 11)) break;
+      if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * TILE_BYTES);
+      __syncwarp();
+      if (row >= 0) {
+        uint8_t* kt = tiles + s * 2 * TILE_BYTES + lane * box_rows * 128;
         uint8_t* vt = kt + TILE_BYTES;
-        const int jb = jb0 + t * KT;
-        for (int b = 0; b < boxes; ++b) {
-          const int key = jb + b * box_rows;
-          const int pg = key / ps;
-          // beyond the request's pages (keys that no row sees): any valid page will do, they are masked
-          const int page = (pg < a.table_stride && key < kv_len) ? max(table[pg], 0) : 0;
-          const int row = (page * a.nkv + kvh) * ps + key % ps;      // row of the [pages*nkv*ps, HD] view
 #pragma unroll
-          for (int p = 0; p < PANELS; ++p) {
-            tma_load_2d_hint(kt + p * (KT * 128) + b * box_rows * 128, &map_k, &full_bar[s], p * 64, row, stream_once);
-            tma_load_2d_hint(vt + p * (KT * 128) + b * box_rows * 128, &map_v, &full_bar[s], p * 64, row, stream_once);
-          }
+        for (int p = 0; p < PANELS; ++p) {
+          tma_load_2d_hint(kt + p * (KT * 128), &map_k, &full_bar[s], p * 64, row, stream_once);
+          tma_load_2d_hint(vt + p * (KT * 128), &map_v, &full_bar[s], p * 64, row, stream_once);
         }
       }
     }
     __syncwarp();
   } else {
-    // ---------------- consumers ----------------
+    // ---------------- consumers: warp w takes keys [16 w, 16 w + 16) of every tile ----------------
+    // Each warp keeps its own running maximum, sum and output over all dims for its keys; the four
+    // are merged once, after the last tile.  No warp repeats another's products.
     uint32_t qf[KS][4];
     {
       const int mi = lane >> 3;
@@ -221,6 +237,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
     const int mi = lane >> 3;
+    const int k_warp = warp * KW;                     // this warp's first key within a tile
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int s = t % STAGES, j = t / STAGES;
@@ -228,29 +245,25 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (!ok) break;
       const uint32_t kt = s32(tiles + s * 2 * TILE_BYTES), vt = kt + TILE_BYTES;
       const int jb = jb0 + t * KT;
-      // scores of all 64 keys
-      float sc[8][4];
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+      // scores of this warp's 16 keys
+      float sc[2][4];
+      sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-        for (int nt = 0; nt < 8; nt += 2) {
-          uint32_t b[4];
-          ldsm4(b, tile_addr(kt, (nt + (mi >> 1)) * 8 + (lane & 7), ks * 2 + (mi & 1)));
-          mma16816(sc[nt], qf[ks], b[0], b[1]);
-          mma16816(sc[nt + 1], qf[ks], b[2], b[3]);
-        }
+        uint32_t b[4];
+        ldsm4(b, tile_addr(kt, k_warp + (mi >> 1) * 8 + (lane & 7), ks * 2 + (mi & 1)));
+        mma16816(sc[0], qf[ks], b[0], b[1]);
+        mma16816(sc[1], qf[ks], b[2], b[3]);
       }
       const bool need_mask = jb + KT > min(slice_hi, start + 1) || a.window > 0;
       float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float v = sc[nt][x] * a.scale_log2;
           if (need_mask) {
-            const int key = jb + nt * 8 + (lane & 3) * 2 + (x & 1);
+            const int key = jb + k_warp + nt * 8 + (lane & 3) * 2 + (x & 1);
             const int pos = x < 2 ? pos0 : pos1, lo = x < 2 ? lo0 : lo1;
             if (key > pos || key < lo || key >= slice_hi) v = -CUDART_INF_F;
           }
@@ -265,90 +278,108 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
       const float base0 = mn0 == -CUDART_INF_F ? 0.f : mn0, base1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
       const float alpha0 = exp2f(m0 - base0), alpha1 = exp2f(m1 - base1);
+      const bool moved = mn0 != m0 || mn1 != m1;
       m0 = mn0;
       m1 = mn1;
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pf[4][4];
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const float p0 = exp2f(sc[nt][0] - base0), p1 = exp2f(sc[nt][1] - base0);
-        const float p2 = exp2f(sc[nt][2] - base1), p3 = exp2f(sc[nt][3] - base1);
-        sum0 += p0 + p1;
-        sum1 += p2 + p3;
-        pf[nt >> 1][(nt & 1) * 2 + 0] = pack2(p0, p1);
-        pf[nt >> 1][(nt & 1) * 2 + 1] = pack2(p2, p3);
+      uint32_t pf[4];
+      {
+        const float p0 = exp2f(sc[0][0] - base0), p1 = exp2f(sc[0][1] - base0);
+        const float p2 = exp2f(sc[0][2] - base1), p3 = exp2f(sc[0][3] - base1);
+        const float p4 = exp2f(sc[1][0] - base0), p5 = exp2f(sc[1][1] - base0);
+        const float p6 = exp2f(sc[1][2] - base1), p7 = exp2f(sc[1][3] - base1);
+        float sum0 = (p0 + p1) + (p4 + p5), sum1 = (p2 + p3) + (p6 + p7);
+        pf[0] = pack2(p0, p1);
+        pf[1] = pack2(p2, p3);
+        pf[2] = pack2(p4, p5);
+        pf[3] = pack2(p6, p7);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        l0 = l0 * alpha0 + sum0;
+        l1 = l1 * alpha1 + sum1;
       }
-      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
-      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-      l0 = l0 * alpha0 + sum0;
-      l1 = l1 * alpha1 + sum1;
+      if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-      for (int dn = 0; dn < NT_O; ++dn) {
-        o[dn][0] *= alpha0; o[dn][1] *= alpha0; o[dn][2] *= alpha1; o[dn][3] *= alpha1;
+        for (int dn = 0; dn < NT_ALL; ++dn) {
+          o[dn][0] *= alpha0; o[dn][1] *= alpha0; o[dn][2] *= alpha1; o[dn][3] *= alpha1;
+        }
       }
       // rows of the V tile that no query sees (past the sequence's end in its last tile, before the
       // window's start in its first) may hold anything: a zero weight times a non-finite value would
-      // still poison the sum, so those rows of this warp's dims are cleared
+      // still poison the sum, so this warp clears those among its keys
       {
         const int bad_from = jb + KT > kv_len ? kv_len - jb : KT;             // rows [bad_from, KT)
         const int bad_to = (a.window > 0 && jb < first_key) ? first_key - jb : 0;   // rows [0, bad_to)
-        if (bad_from < KT || bad_to > 0) {
-          for (int idx = lane; idx < KT * NT_O; idx += 32) {
-            const int key = idx / NT_O, c16 = warp * NT_O + idx % NT_O;
+        if (bad_from < k_warp + KW || bad_to > k_warp) {
+          for (int idx = lane; idx < KW * (HD / 8); idx += 32) {
+            const int key = k_warp + idx / (HD / 8), c16 = idx % (HD / 8);
             if (key >= bad_from || key < bad_to)
               asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(tile_addr(vt, key, c16)), "r"(0) : "memory");
           }
           __syncwarp();
         }
       }
-      // O[:, this warp's dims] += P . V
+      // O += P . V over this warp's keys, all dims
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-#pragma unroll
-        for (int dn = 0; dn < NT_O; dn += 2) {
-          uint32_t b[4];
-          ldsm4_t(b, tile_addr(vt, kk * 16 + (mi & 1) * 8 + (lane & 7), warp * NT_O + dn + (mi >> 1)));
-          mma16816(o[dn], pf[kk], b[0], b[1]);
-          mma16816(o[dn + 1], pf[kk], b[2], b[3]);
-        }
+      for (int dn = 0; dn < NT_ALL; dn += 2) {
+        uint32_t b[4];
+        ldsm4_t(b, tile_addr(vt, k_warp + (mi & 1) * 8 + (lane & 7), dn + (mi >> 1)));
+        mma16816(o[dn], pf, b[0], b[1]);
+        mma16816(o[dn + 1], pf, b[2], b[3]);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
-  }
 
-  // ---------------- output ----------------
-  const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
-  if (warp < CONSUMERS) {
-    const int ra = lane >> 2, rb = ra + 8;
+    // ---------------- the four warps' shares of the block's keys are merged ----------------
+    // every tile has been consumed, so the tile memory is free: [CONSUMERS][16][HD + 8] floats of
+    // scaled partial outputs, then [CONSUMERS][16][2] floats of (maximum, sum)
+    float* o_s = reinterpret_cast<float*>(tiles);
+    float* ml_s = o_s + CONSUMERS * 16 * OS;
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");     // no warp still reads a tile
+    if ((lane & 3) == 0) {
+      *reinterpret_cast<float2*>(ml_s + (warp * 16 + ra) * 2) = make_float2(m0, l0);
+      *reinterpret_cast<float2*>(ml_s + (warp * 16 + rb) * 2) = make_float2(m1, l1);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+    float mm0 = -CUDART_INF_F, mm1 = -CUDART_INF_F;
 #pragma unroll
-    for (int dn = 0; dn < NT_O; ++dn) {
-      const int d = (warp * NT_O + dn) * 8 + (lane & 3) * 2;
+    for (int w = 0; w < CONSUMERS; ++w) {
+      mm0 = fmaxf(mm0, ml_s[(w * 16 + ra) * 2]);
+      mm1 = fmaxf(mm1, ml_s[(w * 16 + rb) * 2]);
+    }
+    const float f0 = exp2f(m0 - (mm0 == -CUDART_INF_F ? 0.f : mm0)), f1 = exp2f(m1 - (mm1 == -CUDART_INF_F ? 0.f : mm1));
+#pragma unroll
+    for (int dn = 0; dn < NT_ALL; ++dn) {
+      const int d = dn * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(o_s + (warp * 16 + ra) * OS + d) = make_float2(o[dn][0] * f0, o[dn][1] * f0);
+      *reinterpret_cast<float2*>(o_s + (warp * 16 + rb) * OS + d) = make_float2(o[dn][2] * f1, o[dn][3] * f1);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+    // the block's output: the warps' shares are added in warp order
+    const size_t slab = ((size_t)e * a.nkv + kvh) * a.nsplit + z;
+    for (int idx = threadIdx.x; idx < rows_total * HD; idx += CONSUMERS * 32) {
+      const int row = idx / HD, d = idx - row * HD;
+      float mm = -CUDART_INF_F;
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) mm = fmaxf(mm, ml_s[(w * 16 + row) * 2]);
+      const float base = mm == -CUDART_INF_F ? 0.f : mm;
+      float ll = 0.f, oo = 0.f;
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) {
+        ll += ml_s[(w * 16 + row) * 2 + 1] * exp2f(ml_s[(w * 16 + row) * 2] - base);
+        oo += o_s[(w * 16 + row) * OS + d];
+      }
       if (a.nsplit == 1) {
-        if (ra < rows_total) {
-          const float inv = l0 > 0.f ? 1.f / l0 : 0.f;
-          *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + ra / g) * a.nq + kvh * g + ra % g) * HD + d) =
-              pack2(o[dn][0] * inv, o[dn][1] * inv);
-        }
-        if (rb < rows_total) {
-          const float inv = l1 > 0.f ? 1.f / l1 : 0.f;
-          *reinterpret_cast<uint32_t*>(a.out + ((size_t)(q0 + rb / g) * a.nq + kvh * g + rb % g) * HD + d) =
-              pack2(o[dn][2] * inv, o[dn][3] * inv);
-        }
+        a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
       } else {
-        if (ra < rows_total)
-          *reinterpret_cast<float2*>(a.part_o + ((slab0 + z) * 16 + ra) * HD + d) = make_float2(o[dn][0], o[dn][1]);
-        if (rb < rows_total)
-          *reinterpret_cast<float2*>(a.part_o + ((slab0 + z) * 16 + rb) * HD + d) = make_float2(o[dn][2], o[dn][3]);
+        a.part_o[(slab * 16 + row) * HD + d] = oo;
+        if (d == 0) *reinterpret_cast<float2*>(a.part_ml + (slab * 16 + row) * 2) = make_float2(mm, ll);
       }
     }
-    if (a.nsplit > 1 && warp == 0 && (lane & 3) == 0) {
-      if (ra < rows_total) *reinterpret_cast<float2*>(a.part_ml + ((slab0 + z) * 16 + ra) * 2) = make_float2(m0, l0);
-      if (rb < rows_total) *reinterpret_cast<float2*>(a.part_ml + ((slab0 + z) * 16 + rb) * 2) = make_float2(m1, l1);
-    }
   }
+  const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
   if (a.nsplit == 1) return;
   __threadfence();
   __syncthreads();
@@ -361,18 +392,39 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // The last block of an (entry, KV head) adds the slices in slice order.  First a warp per row: lane s
+  // takes slice s's (maximum, sum) and the row's weights exp2(m_s - max) / total go to shared memory;
+  // then every thread adds its elements with the loads of all slices in flight together.
+  float* fac = reinterpret_cast<float*>(tiles);            // [16][32]
+  for (int row = warp; row < rows_total; row += THREADS / 32) {
+    float m = -CUDART_INF_F, l = 0.f;
+    if (lane < a.nsplit) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + ((slab0 + lane) * 16 + row) * 2));
+      m = ml.x;
+      l = ml.y;
+    }
+    const float mm = warp_max(m);
+    const float f = exp2f(m - (mm == -CUDART_INF_F ? 0.f : mm));
+    const float ll = warp_sum(l * f);
+    fac[row * 32 + lane] = ll > 0.f ? f / ll : 0.f;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < rows_total * HD; idx += THREADS) {
     const int row = idx / HD, d = idx - row * HD;
-    float mm = -CUDART_INF_F;
-    for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]));
-    const float base = mm == -CUDART_INF_F ? 0.f : mm;
-    float ll = 0.f, oo = 0.f;
-    for (int s = 0; s < a.nsplit; ++s) {
-      const float f = exp2f(__ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2]) - base);
-      ll += __ldcg(&a.part_ml[((slab0 + s) * 16 + row) * 2 + 1]) * f;
-      oo += __ldcg(&a.part_o[((slab0 + s) * 16 + row) * HD + d]) * f;
+    float oo = 0.f;
+    int sl = 0;
+    for (; sl + 4 <= a.nsplit; sl += 4) {
+      const float v0 = __ldcg(&a.part_o[((slab0 + sl) * 16 + row) * HD + d]);
+      const float v1 = __ldcg(&a.part_o[((slab0 + sl + 1) * 16 + row) * HD + d]);
+      const float v2 = __ldcg(&a.part_o[((slab0 + sl + 2) * 16 + row) * HD + d]);
+      const float v3 = __ldcg(&a.part_o[((slab0 + sl + 3) * 16 + row) * HD + d]);
+      oo += v0 * fac[row * 32 + sl];
+      oo += v1 * fac[row * 32 + sl + 1];
+      oo += v2 * fac[row * 32 + sl + 2];
+      oo += v3 * fac[row * 32 + sl + 3];
     }
-    a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+    for (; sl < a.nsplit; ++sl) oo += __ldcg(&a.part_o[((slab0 + sl) * 16 + row) * HD + d]) * fac[row * 32 + sl];
+    a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(oo);
   }
 }
 
@@ -416,7 +468,6 @@ attention_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(q_s + ROWS_PER_BLOCK * (HD + 8));
   uint64_t* empty_bar = full_bar + ROWS_STAGES;
 
-  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < ROWS_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ROWS_CONSUMERS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -424,6 +475,7 @@ attention_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
   }
   pdl_wait();
+  pdl_trigger();
   const int e = a.work[2 * blockIdx.x], rt = a.work[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -704,7 +756,9 @@ extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cach
     return refuse(ST_BAD_SIZE, "attention_decode_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
   if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % dec::KT || (nsplit > 1 && (!part_o || !part_ml || !slice_counters)))
     return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
-  if (nsplit > 65535 || nkv > 65535) return refuse(ST_BAD_SIZE, "attention_decode_tma: grid too large");
+  if (nsplit > 32 || nkv > 65535)
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d nkv=%d (at most 32 slices: the merge gives a lane to each)",
+                  nsplit, nkv);
   const int box_rows = page_size < dec::KT ? page_size : dec::KT;
   const long long rows = num_pages * nkv * page_size;
   const CUtensorMap* mk = dec::cache_map(k_cache, rows, hd, box_rows);

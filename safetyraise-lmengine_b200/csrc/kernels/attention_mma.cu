@@ -234,8 +234,8 @@ attention_rows_kernel(const AttnArgs a) {
   bf16* kv_s = q_s + ROWS_PER_BLOCK * stride;            // [2 stages][K tile | V tile]
   const int tile_elems = KT * stride;
 
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int e = a.work[2 * blockIdx.x], rt = a.work[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
@@ -329,8 +329,8 @@ attention_keys_kernel(const AttnArgs a) {
   bf16* kv_s = q_s + 16 * stride;                           // [stages][K tile | V tile]
   const int tile_elems = KT * stride;
 
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;

@@ -297,8 +297,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   __syncthreads();
   fence_after();
   const uint32_t tmem = *tmem_slot;
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
 
   // the grid runs over (block of rows, KV head) with the heads fastest: the work list is sorted by
   // length, and blocks start in the order of their index

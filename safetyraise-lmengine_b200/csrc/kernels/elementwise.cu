@@ -11,8 +11,8 @@ namespace srlm {
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                     float* __restrict__ out, int H, int vocab, int* __restrict__ bad) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {          // the host checks too; never read outside the table
@@ -31,8 +31,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TA* __res
                                    const float* __restrict__ weight, float eps, TA* __restrict__ out,
                                    const int* __restrict__ rows, int H, int unit_offset) {
   __shared__ float scratch[32];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* res = residual + src * H;
@@ -67,8 +67,8 @@ __device__ __forceinline__ float silu_f(float x) {
 // in[T, 2I]: gate in columns [0, I), up in [I, 2I)  ->  out[T, I]
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ in, TA* __restrict__ out, int I, size_t total) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I, i = idx % I;

@@ -43,11 +43,18 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_ROWS = 16;
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {      // read once: do not keep in L1
+// The weights are read once per step: not kept in L1, and the first to leave L2, which then keeps what is
+// read again between the products (tokens, block tables, norm weights, partial sums).
+__device__ __forceinline__ uint4 ld_stream16(const void* p, uint64_t policy) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
   return v;
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
 __device__ __forceinline__ uint4 ld_cached16(const void* p) {      // the tokens: read by every block
   return __ldg(reinterpret_cast<const uint4*>(p));
@@ -93,14 +100,15 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
   // Two batches of weight loads are kept in flight: the next batch is requested before the current
   // one is multiplied.
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  const uint64_t once = l2_evict_first_policy();
   uint4 a[2][SK_UNROLL], b[2][SK_UNROLL];
   auto load_w = [&](int g, uint4 (&aa)[SK_UNROLL], uint4 (&bb)[SK_UNROLL]) {
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u) {
       const int k = (g + u) * 32;
       const bool in = g + u < g_hi && k + 8 * q < K;        // K is a multiple of 8: a 16-byte piece is whole
-      aa[u] = in ? ld_stream16(wa + k) : zero;
-      bb[u] = in ? ld_stream16(wb + k) : zero;
+      aa[u] = in ? ld_stream16(wa + k, once) : zero;
+      bb[u] = in ? ld_stream16(wb + k, once) : zero;
     }
   };
   load_w(g_lo, a[0], b[0]);

@@ -13,8 +13,8 @@ namespace srlm {
 __global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cos_out,
                                   float* __restrict__ sin_out, int T, int half, double theta,
                                   int rotary_dim) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   const int t = idx / half, i = idx % half;
@@ -36,8 +36,8 @@ __global__ void qk_norm_rope_append_kernel(
     float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     const int* __restrict__ kv_slot, int T, int nq, int nkv, int hd, int rotary_half,
     int heads_total, int write_kv, int page_size) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= T * heads_total) return;

@@ -347,9 +347,11 @@ class KernelLibrary:
 
     @staticmethod
     def attention_split(n_entries: int, nkv: int, max_kv: int):
-        """(nsplit, kv_chunk) for the keys-split kernel: enough blocks to fill the GPU, slices of whole tiles."""
+        """(nsplit, kv_chunk) for the keys-split kernels: as many blocks as run at the same time (two per
+        SM) and no more -- a few blocks left over for a second wave would double the time -- in slices of
+        whole tiles."""
         tiles = max(1, (max_kv + 63) // 64)
-        nsplit = max(1, min(tiles, -(-296 // max(1, n_entries * nkv)), 32))
+        nsplit = max(1, min(tiles, 296 // max(1, n_entries * nkv), 32))
         chunk = -(-tiles // nsplit) * 64
         nsplit = -(-tiles * 64 // chunk)
         return nsplit, chunk
