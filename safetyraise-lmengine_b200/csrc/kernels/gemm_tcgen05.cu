@@ -165,7 +165,7 @@ struct GemmArgs {
   long long ldc;
   int* err_flag;
   int kb_per_split;        // k blocks each split handles
-  float* partial;          // [splits, M, N] float32 (split-K only)
+  float* partial;          // [splits, tiles, 128, BN] float32 (split-K only)
   int* tile_counters;      // one per output tile, zero on entry (split-K only)
   int swiglu8;             // 1: weight rows come in blocks of 16 (8 gate rows, then the 8 up rows of the same
                            //    features); the output is silu(gate) * up, [M, N/2]
@@ -297,22 +297,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int n = n0 + lane_base + lane;
     constexpr int CH = BN < 32 ? 16 : 32;
     const bool split = gridDim.z > 1;
+    // split-K: the partial sums of a tile lie as [split][tile][128 weight rows][BN tokens], so a thread
+    // (one weight row) writes and reads its tokens as whole 16-byte pieces
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const size_t tile_floats = (size_t)BM * BN;
+    float* mine = split ? args.partial + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile) * tile_floats +
+                              (size_t)(lane_base + lane) * BN
+                        : nullptr;
     if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
         uint32_t v[CH];
         tmem_load<CH>(tmem_base + ((uint32_t)lane_base << 16) + c, v);
         tmem_load_wait();
+        if (split) {
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int m = m0 + c + j;
-          if (m < args.M) {                                  // the same for every lane
-            const float x = __uint_as_float(v[j]);
-            if (split) {
-              if (n < args.N) args.partial[((size_t)blockIdx.z * args.M + m) * args.N + n] = x;
-            } else {
-              store_result(args, m, n, x, n < args.N);
-            }
+          for (int j = 0; j < CH; j += 4)
+            *reinterpret_cast<uint4*>(mine + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const int m = m0 + c + j;
+            if (m < args.M) store_result(args, m, n, __uint_as_float(v[j]), n < args.N);      // the same m for every lane
           }
         }
       }
@@ -323,7 +329,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         const int prev = atomicAdd(&args.tile_counters[tile], 1);
         *last_flag = (prev == (int)gridDim.z - 1);
         if (*last_flag) args.tile_counters[tile] = 0;
@@ -332,20 +337,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (*last_flag) {
         __threadfence();
         const int rows = min(BN, args.M - m0), nz = (int)gridDim.z;
-        const size_t slab = (size_t)args.M * args.N;
+        const size_t split_floats = (size_t)gridDim.x * gridDim.y * tile_floats;
         const bool have = n < args.N;
-        // 64 rows per round: each round is one trip to L2 with 64 loads in flight per thread, and
-        // there are as many rounds as splits (the sum order stays: split 0, 1, 2, ...)
-        constexpr int RB = 64;
+        // 16 tokens at a time, four splits at a time: one trip to L2 with sixteen 16-byte loads in
+        // flight per thread (the loads are gathered first: folded into the additions they would be
+        // issued one behind the other); the additions run in split order
+        constexpr int RB = 16, ZB = 4;
+        const float* first = args.partial + (size_t)tile * tile_floats + (size_t)(lane_base + lane) * BN;
         for (int j = 0; j < rows; j += RB) {
           float x[RB];
 #pragma unroll
           for (int u = 0; u < RB; ++u) x[u] = 0.f;
-          if (have) {
-            for (int z = 0; z < nz; ++z) {
+          for (int z0 = 0; z0 < nz; z0 += ZB) {
+            float4 t[ZB][RB / 4];
 #pragma unroll
-              for (int u = 0; u < RB; ++u)
-                if (j + u < rows) x[u] += __ldcg(&args.partial[z * slab + (size_t)(m0 + j + u) * args.N + n]);
+            for (int zz = 0; zz < ZB; ++zz) {
+              const float* src = first + j + (size_t)min(z0 + zz, nz - 1) * split_floats;
+#pragma unroll
+              for (int u = 0; u < RB / 4; ++u) t[zz][u] = __ldcg(reinterpret_cast<const float4*>(src) + u);
+            }
+#pragma unroll
+            for (int zz = 0; zz < ZB; ++zz) {
+              if (z0 + zz < nz) {
+#pragma unroll
+                for (int u = 0; u < RB / 4; ++u) {
+                  x[4 * u] += t[zz][u].x; x[4 * u + 1] += t[zz][u].y;
+                  x[4 * u + 2] += t[zz][u].z; x[4 * u + 3] += t[zz][u].w;
+                }
+              }
             }
           }
 #pragma unroll
@@ -642,7 +661,7 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
 using namespace srlm;
 
 // workspace (only when splits > 1): one int per output tile, zero on entry and left zero on exit,
-// at the start; float32 partials [splits, M, N] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
+// at the start; float32 partials [splits, tiles, 128, token tile] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
 extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                     long long ldx, long long ldw, long long ldc, int splits, void* workspace,
                                     long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
@@ -665,7 +684,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0};
   if (splits > 1) {
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-    const long long need = 65536 + (long long)splits * M * N * 4;
+    const long long need = 65536 + (long long)splits * tiles * BM * bn * 4;
     if (!workspace || workspace_bytes < need || tiles * 4 > 65536)
       return refuse(ST_BAD_SIZE, "gemm_tcgen05: split-K with %d splits needs %lld bytes of workspace, got %lld",
                     splits, need, workspace_bytes);
@@ -690,8 +709,8 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
       if (st16 == 12) return launch<16, 12>(mw, mx, a, splits, stream);
       return launch<16, 4>(mw, mx, a, splits, stream);
     }
-    case 32: return launch<32, 3>(mw, mx, a, splits, stream);
-    case 64: return launch<64, 3>(mw, mx, a, splits, stream);
+    case 32: return launch<32, 5>(mw, mx, a, splits, stream);
+    case 64: return launch<64, 4>(mw, mx, a, splits, stream);
     case 128: return launch<128, 3>(mw, mx, a, splits, stream);
     default: return launch<256, 4>(mw, mx, a, splits, stream);
   }
