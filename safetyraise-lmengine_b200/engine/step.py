@@ -56,7 +56,7 @@ class Engine:
         self.steps_run = 0
         # decode-only steps (one token per entry) are recorded into CUDA graphs, one per
         # (batch size, wanted rows, block-table width); the second step of a kind records, later ones replay
-        self.use_graphs = bool(mctx.options.get("cuda_graphs", True))
+        self.use_graphs = bool(mctx.options.get("cuda_graphs", True)) and getattr(model, "replayable", True)
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: set = set()
         self.graph_replays = 0

@@ -145,6 +145,12 @@ class NormedInput:
 class Part:
     """Common behaviour: a part declares its tensors before it is built."""
 
+    # Whether the kernels a forward launches depend on the step's device tensors only (block tables,
+    # positions, slots), not on its host lists.  Decode-only steps of a model whose parts all say so
+    # are recorded into CUDA graphs and replayed; a part that loops over ``ctx.host`` or branches on
+    # values of the step sets this to False and its model always runs eagerly.
+    replayable = True
+
     @classmethod
     def tensor_decls(cls, spec, prefix: str) -> List[TensorDecl]:
         return []

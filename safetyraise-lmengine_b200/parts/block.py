@@ -29,6 +29,8 @@ class PreNormBlock(Part):
         self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
             spec.feed_forward, p, tensors, mctx)
         self.hidden = spec.mixer_norm.size
+        self.replayable = all(getattr(part, "replayable", True)
+                              for part in (self.mixer_norm, self.ff_norm, self.mixer, self.feed_forward))
 
     @classmethod
     def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:

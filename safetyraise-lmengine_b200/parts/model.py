@@ -43,6 +43,9 @@ class DecoderModel:
             if not 0 <= step.layer < len(self.blocks):
                 raise ConfigError(f"run order names layer {step.layer}, the model has {len(self.blocks)}")
         self.bad_flag = torch.zeros(1, dtype=torch.int32, device=mctx.device)
+        # decode steps may be replayed from CUDA graphs only if no part plans on the host
+        self.replayable = all(getattr(b, "replayable", True) for b in self.blocks) and \
+            getattr(self.final_norm, "replayable", True)
 
     def cache_groups(self) -> List[CacheGroupSpec]:
         """Run steps with equal needs share a group; each group gets pages (or state) of its own."""
