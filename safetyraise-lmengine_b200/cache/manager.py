@@ -69,7 +69,7 @@ def runtime():
         lib.srlm_sched_plan.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int64),
                                         C.POINTER(C.c_int)]
         lib.srlm_sched_advance.argtypes = [C.c_void_p, C.c_int64, C.c_int]
-        for name in ("rollback", "append_token", "finish"):
+        for name in ("rollback", "append_token", "retract_token", "finish"):
             getattr(lib, "srlm_sched_" + name).argtypes = [C.c_void_p, C.c_int64]
         lib.srlm_sched_has_work.argtypes = [C.c_void_p]
         lib.srlm_sched_counters.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]

@@ -71,6 +71,7 @@ int srlm_sched_plan(void* s, int64_t* entries, int cap, int64_t* preempted, int*
 int srlm_sched_advance(void* s, int64_t id, int count) { return static_cast<Scheduler*>(s)->advance(id, count); }
 int srlm_sched_rollback(void* s, int64_t id) { return static_cast<Scheduler*>(s)->rollback(id); }
 int srlm_sched_append_token(void* s, int64_t id) { return static_cast<Scheduler*>(s)->append_token(id); }
+int srlm_sched_retract_token(void* s, int64_t id) { return static_cast<Scheduler*>(s)->retract_token(id); }
 int srlm_sched_finish(void* s, int64_t id) { return static_cast<Scheduler*>(s)->finish(id); }
 int srlm_sched_has_work(void* s) { return static_cast<Scheduler*>(s)->has_work() ? 1 : 0; }
 void srlm_sched_counters(void* s, int64_t* out) {

@@ -35,6 +35,7 @@ int srlm_sched_plan(void* sched, int64_t* entries, int cap, int64_t* preempted, 
 int srlm_sched_advance(void* sched, int64_t id, int count);
 int srlm_sched_rollback(void* sched, int64_t id);
 int srlm_sched_append_token(void* sched, int64_t id);
+int srlm_sched_retract_token(void* sched, int64_t id);
 int srlm_sched_finish(void* sched, int64_t id);
 int srlm_sched_has_work(void* sched);
 /* out[9]: submitted rejected completed preempted steps batched_tokens generated_tokens active queued */

@@ -158,6 +158,16 @@ int Scheduler::append_token(int64_t id) {
   return r.total_len - r.prompt_len;
 }
 
+int Scheduler::retract_token(int64_t id) {
+  auto it = requests_.find(id);
+  if (it == requests_.end()) return -1;
+  Request& r = it->second;
+  if (r.total_len <= r.prompt_len || r.fed >= r.total_len) return -2;   // nothing counted that was not fed yet
+  r.total_len -= 1;
+  counters_.generated_tokens -= 1;
+  return r.total_len - r.prompt_len;
+}
+
 int Scheduler::finish(int64_t id) {
   auto it = requests_.find(id);
   if (it == requests_.end()) return -1;

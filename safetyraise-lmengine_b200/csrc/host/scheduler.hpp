@@ -68,6 +68,7 @@ class Scheduler {
   int advance(int64_t id, int count);   // the step ran: count more tokens are in the cache
   int rollback(int64_t id);             // the step failed: give back what plan() reserved
   int append_token(int64_t id);         // one sampled token joined the request
+  int retract_token(int64_t id);        // the token counted last turned out not to join it (a stop token)
   int finish(int64_t id);               // any reason: frees pages and slot, forgets the request
   bool has_work() const { return !running_.empty() || !queue_.empty(); }
   Counters counters() const;

@@ -20,7 +20,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, fresh_seed
 from .scheduler import (FINISH_CANCELLED, FINISH_DEADLINE, FINISH_ERROR, FINISH_LENGTH, FINISH_STOP,
                         GenerationRequest, RequestState, Scheduler, Usage)
-from .step import Engine, StepEntry
+from .step import LATER, Engine, StepEntry
 
 
 @dataclass
@@ -37,6 +37,7 @@ class EngineConfig:
     num_pages: Optional[int] = None        # None: sized from free device memory
     dtype: str = "bfloat16"
     device: str = "cuda:0"
+    plan_ahead: bool = True                # the next decode step's host work runs while the device works
 
     def validate(self) -> None:            # src/engine/scheduler.rs:124-141
         for name in ("max_context", "max_active", "queue_capacity", "prefill_chunk", "max_request_ms",
@@ -78,6 +79,7 @@ class LLM:
         self._done: Dict[int, RequestState] = {}
         self._ids = itertools.count(1)
         self.failed = self.cancelled = 0
+        self._prepared = None          # (plan, PreparedStep, open token places) of a step laid out ahead
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -134,54 +136,131 @@ class LLM:
         self._done[rid] = st
 
     # ---- the loop ---------------------------------------------------------------------
+    def _discard_prepared(self) -> None:
+        """Takes back a step that was prepared ahead and will not run as planned."""
+        if self._prepared is None:
+            return
+        plan, prep, _ = self._prepared
+        self._prepared = None
+        self.engine.discard(prep)
+        for p in plan:
+            self.scheduler.rollback(p.request_id)
+
+    def _fail_plan(self, plan, error: Exception) -> None:
+        for p in plan:                                 # src/engine/scheduler.rs:882-895
+            self.scheduler.rollback(p.request_id)
+            self._finish(p.request_id, FINISH_ERROR, str(error))
+
+    def _plan_ahead(self, plan, sampled, states) -> bool:
+        """While the device runs a decode step, does the host half of the next one: bookkeeping of this
+        step, the scheduler's plan, page reservation and batch layout, with the ids of the tokens being
+        sampled left open.  Only when no token value can change the plan: every entry decodes, nobody
+        waits in the queue, nobody reaches its length.  A stop token still can: then the prepared step
+        is taken back.  Returns whether this step's bookkeeping (advance, append_token) was done."""
+        if not self.config.plan_ahead or len(sampled) != len(plan) or any(p.count != 1 for p in plan):
+            return False
+        if self.scheduler.counters()["queued"]:
+            return False
+        for st in states:
+            if len(st.tokens) - st.usage.prompt_tokens + 1 >= st.request.sampling.max_new_tokens:
+                return False
+        for p in plan:
+            self.scheduler.advance(p.request_id, p.count)
+            self.scheduler.append_token(p.request_id)
+        nxt, preempted = self.scheduler.plan()
+        for rid in preempted:
+            self._live[rid].usage.preemptions += 1
+        if not nxt:
+            return True
+        entries, later = [], []
+        for i, p in enumerate(nxt):
+            st = self._live[p.request_id]
+            known = len(st.tokens)                     # the token being sampled will sit at this index
+            toks = [st.tokens[j] if j < known else LATER for j in range(p.start, p.start + p.count)]
+            if p.start + p.count > known:
+                later.append((i, known - p.start, p.request_id))
+            entries.append(StepEntry(p.slot, toks, [p.count - 1] if p.want_logits else []))
+        try:
+            prep = self.engine.prepare(entries)
+        except EngineError:
+            for p in nxt:                              # planned normally at the next turn
+                self.scheduler.rollback(p.request_id)
+            return True
+        self._prepared = (nxt, prep, later)
+        return True
+
     def step(self, on_token: Optional[Callable[[int, int, int], None]] = None) -> bool:
         """One scheduler turn: interruptions, plan, one engine step, sampling.  False when idle."""
         now = time.monotonic()
         for rid, st in list(self._live.items()):      # checked between steps only
-            if st.cancelled:
-                self._finish(rid, FINISH_CANCELLED)
-            elif st.deadline_at is not None and now >= st.deadline_at:
-                self._finish(rid, FINISH_DEADLINE)
-        if not self.scheduler.has_work():
-            return False
-        plan, preempted = self.scheduler.plan()
-        for rid in preempted:
-            self._live[rid].usage.preemptions += 1
-        if not plan:
-            return self.scheduler.has_work() and bool(self._live)
-        entries = []
+            reason = FINISH_CANCELLED if st.cancelled else \
+                FINISH_DEADLINE if st.deadline_at is not None and now >= st.deadline_at else None
+            if reason is not None:
+                self._discard_prepared()
+                self._finish(rid, reason)
+        if self._prepared is not None:
+            plan, prep, _ = self._prepared
+            self._prepared = None
+        else:
+            if not self.scheduler.has_work():
+                return False
+            plan, preempted = self.scheduler.plan()
+            for rid in preempted:
+                self._live[rid].usage.preemptions += 1
+            if not plan:
+                return self.scheduler.has_work() and bool(self._live)
+            entries = []
+            for p in plan:
+                st = self._live[p.request_id]
+                entries.append(StepEntry(p.slot, st.tokens[p.start:p.start + p.count],
+                                         [p.count - 1] if p.want_logits else []))
+            try:
+                prep = self.engine.prepare(entries)
+            except EngineError as e:
+                self._fail_plan(plan, e)
+                return True
         for p in plan:
             st = self._live[p.request_id]
             if st.first_step_at is None:
                 st.first_step_at = now
                 st.usage.queue_ms = (now - st.submitted_at) * 1000.0
-            entries.append(StepEntry(p.slot, st.tokens[p.start:p.start + p.count],
-                                     [p.count - 1] if p.want_logits else []))
         try:
-            logits = self.engine.step(entries)
+            logits = self.engine.run(prep)
         except EngineError as e:
-            for p in plan:                             # src/engine/scheduler.rs:882-895
-                self.scheduler.rollback(p.request_id)
-                self._finish(p.request_id, FINISH_ERROR, str(e))
+            self._fail_plan(plan, e)
             return True
         sampled = [p for p in plan if p.want_logits]
         states = [self._live[p.request_id] for p in sampled]
-        tokens = self.sampler.sample(
+        rows = self.sampler.launch(
             logits, [s.request.sampling for s in states], [s.seed for s in states],
             [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
-        for p in plan:
-            self.scheduler.advance(p.request_id, p.count)
+        ahead = self._plan_ahead(plan, sampled, states)        # overlaps the device's work
+        tokens = self.sampler.collect(rows)                     # waits for the device
+        if not ahead:
+            for p in plan:
+                self.scheduler.advance(p.request_id, p.count)
+        stopped = [p.request_id for p, tok in zip(sampled, tokens) if tok in self.eos]
+        if ahead and stopped:
+            self._discard_prepared()                   # a stop token changes who decodes next
+        by_rid = {}
         for p, st, tok in zip(sampled, states, tokens):
             rid = p.request_id
             if tok in self.eos:                        # the stop token is neither kept nor fed
+                if ahead:
+                    self.scheduler.retract_token(rid)
                 self._finish(rid, FINISH_STOP)
                 continue
             st.tokens.append(tok)
-            n = self.scheduler.append_token(rid)
+            by_rid[rid] = tok
+            n = len(st.tokens) - st.usage.prompt_tokens if ahead else self.scheduler.append_token(rid)
             if on_token is not None:
                 on_token(rid, tok, n - 1)
             if n >= st.request.sampling.max_new_tokens:
                 self._finish(rid, FINISH_LENGTH)       # no forward for a token nobody will read
+        if self._prepared is not None:
+            _, nxt_prep, later = self._prepared
+            for entry, index, rid in later:
+                nxt_prep.set_token(entry, index, by_rid[rid])
         return True
 
     def run_until_idle(self, on_token=None) -> None:

@@ -114,6 +114,10 @@ class Scheduler:
     def append_token(self, request_id: int) -> int:
         return self._lib.srlm_sched_append_token(self._h, request_id)
 
+    def retract_token(self, request_id: int) -> int:
+        """Undoes the last append_token of a request whose token was not fed yet (it was a stop token)."""
+        return self._lib.srlm_sched_retract_token(self._h, request_id)
+
     def finish(self, request_id: int) -> None:
         self._lib.srlm_sched_finish(self._h, request_id)
 

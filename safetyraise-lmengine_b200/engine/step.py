@@ -30,11 +30,38 @@ DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfl
           "bf16": torch.bfloat16}
 
 
+LATER = -1      # a token id that is filled in between prepare() and run()
+
+
 @dataclass
 class StepEntry:
     slot: int
-    tokens: Sequence[int]
+    tokens: Sequence[int]             # LATER for an id that PreparedStep.set_token supplies before run()
     want: Sequence[int] = ()          # indices into ``tokens`` whose logits are returned
+
+
+@dataclass
+class PreparedStep:
+    """A step whose host work is done: checked, pages reserved, the batch laid out in a pinned buffer.
+    Nothing has been copied to the device or launched yet."""
+    entries: Sequence[StepEntry]
+    starts: List[int]
+    q_lens: List[int]
+    kv_lens: List[int]
+    sections: dict
+    words: int
+    pair: list                        # [pinned host buffer, event of its last copy]
+    pages: int
+    wanted: int
+    token_at: List[int]               # offset of each entry's first token id in the buffer
+    missing: int                      # token ids still to be set
+
+    def set_token(self, entry: int, index: int, token: int) -> None:
+        h = self.pair[0].numpy()
+        at = self.token_at[entry] + index
+        if h[at] == LATER:
+            self.missing -= 1
+        h[at] = token
 
 
 def _round_up(a: int, b: int) -> int:
@@ -122,7 +149,7 @@ class Engine:
             if start + n > self.max_context:
                 raise ShapeError(f"slot {e.slot}: {start}+{n} tokens exceed the context of {self.max_context}")
             for t in e.tokens:
-                if not 0 <= int(t) < vocab:
+                if not 0 <= int(t) < vocab and int(t) != LATER:
                     raise ShapeError(f"token id {t} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
@@ -146,8 +173,8 @@ class Engine:
             pair[1].synchronize()
         return pair, self._meta_dev
 
-    def build_context(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
-        """Flattens the batch, uploads it in one copy and returns the device views."""
+    def _lay_out(self, entries: Sequence[StepEntry], starts: List[int]) -> PreparedStep:
+        """Flattens the batch into a pinned host buffer (no device work)."""
         n = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
@@ -174,19 +201,22 @@ class Engine:
         place("logit_rows", R)
         for g in groups:
             place("table:" + g.name, n * pages)
-        pair, dev = self._meta_buffers(off)
-        host = pair[0]
-        h = host.numpy()
+        pair, _ = self._meta_buffers(off)
+        h = pair[0].numpy()
         view = lambda name: h[sections[name][0]:sections[name][0] + sections[name][1]]
         tok, posv, eot = view("token_ids"), view("positions"), view("entry_of_token")
         cu = view("cu_q")
         rows = view("logit_rows")
         cu[0] = 0
         t0 = r0 = 0
+        token_at, missing = [], 0
         tables = {g.name: [self.cache.table(g.name, e.slot) for e in entries] for g in groups}
         for i, e in enumerate(entries):
             q = q_lens[i]
-            tok[t0:t0 + q] = np.asarray(e.tokens, dtype=np.int32)
+            ids = np.asarray(e.tokens, dtype=np.int32)
+            missing += int((ids == LATER).sum())
+            token_at.append(sections["token_ids"][0] + t0)
+            tok[t0:t0 + q] = ids
             posv[t0:t0 + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
             eot[t0:t0 + q] = i
             for w in e.want:
@@ -203,20 +233,35 @@ class Engine:
             cu[i + 1] = t0
         view("slots")[:] = [e.slot for e in entries]
         view("kv_lens")[:] = kv_lens
-        dev[:off].copy_(host[:off], non_blocking=True)
+        return PreparedStep(entries=entries, starts=starts, q_lens=q_lens, kv_lens=kv_lens, sections=sections,
+                            words=off, pair=pair, pages=pages, wanted=R, token_at=token_at, missing=missing)
+
+    def _upload(self, prep: PreparedStep) -> StepContext:
+        """Copies the laid-out batch to the device in one copy and returns the device views."""
+        sections, off, pair = prep.sections, prep.words, prep.pair
+        dev = self._meta_dev
+        dev[:off].copy_(pair[0][:off], non_blocking=True)
         self.last_h2d_bytes = off * 4
         pair[1] = torch.cuda.Event()
         pair[1].record()
+        groups = self.cache.paged_groups
+        n, pages = len(prep.entries), prep.pages
         d = lambda name: dev[sections[name][0]:sections[name][0] + sections[name][1]]
         return StepContext(
-            T=T, n_entries=n, token_ids=d("token_ids"), positions=d("positions"),
+            T=sum(prep.q_lens), n_entries=n, token_ids=d("token_ids"), positions=d("positions"),
             entry_of_token=d("entry_of_token"), slots=d("slots"), cu_q=d("cu_q"), kv_lens=d("kv_lens"),
             logit_rows=d("logit_rows"),
             block_tables={g.name: d("table:" + g.name).view(n, pages) for g in groups},
             kv_slot={g.name: d("kv_slot:" + g.name) for g in groups},
-            host={"q_lens": q_lens, "starts": starts, "kv_lens": kv_lens, "slots": [e.slot for e in entries]},
+            host={"q_lens": prep.q_lens, "starts": prep.starts, "kv_lens": prep.kv_lens,
+                  "slots": [e.slot for e in prep.entries]},
             cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens), kv_bound=pages * ps, options=self.mctx.options)
+            max_q_len=max(prep.q_lens), max_kv_len=max(prep.kv_lens), kv_bound=pages * self.cache.page_size,
+            options=self.mctx.options)
+
+    def build_context(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
+        """Flattens the batch, uploads it in one copy and returns the device views."""
+        return self._upload(self._lay_out(entries, starts))
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         """Runs the model on the batch: eagerly, or by replaying the CUDA graph of this kind of step."""
@@ -247,8 +292,10 @@ class Engine:
         self.graph_replays += 1
         return logits
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""
+    def prepare(self, entries: Sequence[StepEntry]) -> PreparedStep:
+        """The host half of a step: checks, page reservation, batch layout.  Token ids given as LATER
+        may be supplied afterwards (``PreparedStep.set_token``).  Between prepare() and run() or
+        discard() of a step no other step may be prepared or run."""
         self._validate(entries)
         starts = [self.cache.length(e.slot) for e in entries]
         done = []
@@ -261,13 +308,35 @@ class Engine:
             done.append((e, s))
         try:
             with torch.cuda.device(self.mctx.device):
-                ctx = self.build_context(entries, starts)
-                logits = self._forward(ctx)
+                return self._lay_out(entries, starts)
         except Exception:
-            for e, s in done:
-                self.cache.truncate(e.slot, s)
+            self.discard_reservation(entries, starts)
             raise
-        for e, s in done:
+
+    def discard_reservation(self, entries, starts) -> None:
+        for e, s in zip(entries, starts):
+            self.cache.truncate(e.slot, s)
+
+    def discard(self, prep: PreparedStep) -> None:
+        """Gives back what a prepared step reserved; nothing of it ran."""
+        self.discard_reservation(prep.entries, prep.starts)
+
+    def run(self, prep: PreparedStep) -> torch.Tensor:
+        """The device half: one copy of the layout, the forward, the new lengths."""
+        if prep.missing:
+            self.discard(prep)
+            raise ShapeError(f"{prep.missing} token ids of the prepared step were never set")
+        try:
+            with torch.cuda.device(self.mctx.device):
+                logits = self._forward(self._upload(prep))
+        except Exception:
+            self.discard(prep)
+            raise
+        for e, s in zip(prep.entries, prep.starts):
             self.cache.commit(e.slot, s + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""
+        return self.run(self.prepare(entries))

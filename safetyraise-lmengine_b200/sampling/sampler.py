@@ -56,13 +56,23 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
         """logits [n, V] float32 on the device; one token id per row, as Python ints."""
+        return self.collect(self.launch(logits, params, seeds, indices, histories))
+
+    def collect(self, n: int) -> List[int]:
+        """The tokens of the last launch(): waits for the device and reads them back."""
+        return self._out[:n].tolist() if n else []
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               indices: Sequence[int], histories: Sequence[Sequence[int]]) -> int:
+        """Starts the sampling kernel for the rows of ``logits``; returns the number of rows.  The host
+        does not wait: collect() does."""
         n = logits.shape[0]
         if n == 0:
-            return []
+            return 0
         self._grow(n)
         if all(p.is_greedy for p in params):
             ops.argmax(logits, self._out[:n], self.bad)
-            return self._out[:n].tolist()
+            return n
         h = self._host.numpy()
         c = self._cap
         for i, p in enumerate(params):
@@ -85,4 +95,4 @@ class Sampler:
             offs = torch.tensor(offsets, dtype=torch.int32, device=self.device)
         ops.sample(logits, d[:n], d[4 * c:4 * c + n].view(torch.int32), d[c:c + n], d[2 * c:2 * c + n],
                    d[3 * c:3 * c + n], hist, offs, self._out[:n], self.bad)
-        return self._out[:n].tolist()
+        return n

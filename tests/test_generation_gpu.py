@@ -59,6 +59,48 @@ def test_greedy_generation_matches_plain(tiny_folder, dtype):
     assert llm.engine.cache.audit() == 0 and llm.engine.cache.free_pages() == 64
 
 
+def test_planning_ahead_changes_no_token_and_no_count(folder_b):
+    """The host half of the next decode step runs while the device works (the default); with a stop
+    token among the samples, with seeds, with more requests than slots and with few pages the tokens,
+    finish reasons and counters are those of the plain order of work."""
+    from safetyraise_lmengine_b200 import SamplingParams
+    from safetyraise_lmengine_b200.engine.scheduler import GenerationRequest
+    rng = np.random.default_rng(5)
+    prompts = [random_tokens(rng, n, 100) for n in (9, 14, 3, 21, 6, 12)]
+
+    def run(ahead, stop, **kw):
+        llm = make_llm(folder_b, "float32", plan_ahead=ahead, **kw)
+        llm.eos = set(stop)
+        ids = []
+        for i, pr in enumerate(prompts):
+            sp = SamplingParams(temperature=0.0 if i % 2 == 0 else 0.9, top_k=20, top_p=0.9, seed=100 + i,
+                                repetition_penalty=1.0 if i % 3 else 1.2, max_new_tokens=10 + i)
+            ids.append(llm.submit(GenerationRequest(pr, sp)))
+        seen = []
+        llm.run_until_idle(lambda rid, tok, n: seen.append((rid, tok, n)))
+        out = [llm.take_result(i) for i in ids]
+        m = llm.metrics()
+        assert llm.engine.cache.audit() == 0 and llm.engine.cache.free_pages() == llm.engine.cache.num_pages
+        return [(r.tokens, r.finish_reason, r.usage.completion_tokens) for r in out], seen, \
+            {k: m[k] for k in ("completed", "generated_tokens", "active", "queued")}, llm
+
+    plain, seen0, m0, _ = run(False, ())
+    ahead, seen1, m1, llm = run(True, ())
+    assert ahead == plain and seen1 == seen0 and m1 == m0
+    assert all(reason == "length" for _, reason, _ in plain)
+    # a token that the second and the fourth request generate midway becomes the stop token
+    stop = {plain[1][0][4], plain[3][0][7]}
+    plain_s, seen0, m0, _ = run(False, stop)
+    ahead_s, seen1, m1, _ = run(True, stop)
+    assert ahead_s == plain_s and seen1 == seen0 and m1 == m0
+    assert any(reason == "stop" for _, reason, _ in plain_s)
+    # few pages: requests are preempted and recomputed while steps are laid out ahead
+    plain_p, _, m0, _ = run(False, stop, num_pages=14)
+    ahead_p, _, m1, llm = run(True, stop, num_pages=14)
+    assert ahead_p == plain_p and m1 == m0
+    assert [t for t, _, _ in plain_p] == [t for t, _, _ in plain_s]
+
+
 def test_preemption_and_recompute_give_the_same_tokens(folder_b):
     from safetyraise_lmengine_b200 import SamplingParams
     cfg, _ = TINY["B"]

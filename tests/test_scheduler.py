@@ -145,3 +145,23 @@ def test_every_request_ends_under_pressure():
         assert cache.audit() == 0
     assert finished == set(want) and cache.free_pages("kv") == 6
     assert s.counters()["preempted"] > 0
+
+
+def test_retract_token_undoes_an_unfed_token():
+    """A token that was counted before its value was known (the next step is laid out while the device
+    still samples) and turns out to be a stop token is taken back: lengths and counters as before."""
+    cache, sched = make(num_pages=8, page=4)
+    sched.submit(1, 5, 4)
+    plan, _ = sched.plan()
+    assert [(p.start, p.count, p.want_logits) for p in plan] == [(0, 5, True)]
+    sched.advance(1, 5)
+    assert sched.append_token(1) == 1
+    before = sched.counters()["generated_tokens"]
+    assert sched.retract_token(1) == 0
+    assert sched.counters()["generated_tokens"] == before - 1
+    assert sched.retract_token(1) < 0                     # nothing left to take back
+    assert sched.append_token(1) == 1                     # and it can be counted again
+    plan, _ = sched.plan()
+    assert [(p.start, p.count) for p in plan] == [(5, 1)]
+    sched.finish(1)
+    assert cache.audit() == 0
