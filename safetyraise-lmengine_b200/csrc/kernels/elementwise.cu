@@ -57,6 +57,60 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TA* __res
   }
 }
 
+// The same with rows of H = 4 * k elements read and written as 16-byte (float32) and 8-byte (bfloat16)
+// pieces; a thread keeps up to CACHE pieces in registers, so a row of up to 4 * CACHE * blockDim elements
+// is read once.  The sum of squares adds a thread's elements in index order, then the threads in the
+// order of block_sum: fixed by the width.
+template <int CACHE>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ delta, const float* __restrict__ weight,
+                       float eps, bf16* __restrict__ out, const int* __restrict__ rows, int H, int unit_offset) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float4* res = reinterpret_cast<float4*>(residual + src * H);
+  const uint2* del = delta ? reinterpret_cast<const uint2*>(delta + src * H) : nullptr;
+  const int pieces = H / 4;
+  float4 x[CACHE];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CACHE; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < pieces) {
+      float4 v = res[i];
+      if (del) {
+        const uint2 d = del[i];
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d.y));
+        v.x += lo.x; v.y += lo.y; v.z += hi.x; v.w += hi.y;
+        if (!rows) res[i] = v;
+      }
+      ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+      x[c] = v;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  uint2* o = reinterpret_cast<uint2*>(out + (size_t)r * H);
+  const float4* w4 = reinterpret_cast<const float4*>(weight);
+  const float off = unit_offset ? 1.f : 0.f;
+#pragma unroll
+  for (int c = 0; c < CACHE; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < pieces) {
+      const float4 w = w4[i];
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(x[c].x * inv * (w.x + off), x[c].y * inv * (w.y + off));
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(x[c].z * inv * (w.z + off), x[c].w * inv * (w.w + off));
+      uint2 p;
+      p.x = *reinterpret_cast<const uint32_t*>(&lo);
+      p.y = *reinterpret_cast<const uint32_t*>(&hi);
+      o[i] = p;
+    }
+  }
+}
+
 __device__ __forceinline__ float silu_f(float x) {
   // branch-stable logistic, src/model/math.rs:11-22
   if (x >= 0.f) return x / (1.f + expf(-x));
@@ -120,6 +174,24 @@ extern "C" int srlm_add_rmsnorm(float* residual, const void* delta, const float*
                                 cudaStream_t stream) {
   if (R <= 0) return ST_OK;
   if (H <= 0 || !(eps > 0.f)) return refuse(ST_BAD_SIZE, "add_rmsnorm: H=%d eps=%g", H, (double)eps);
+  if (act_dtype == DT_BF16 && H % 4 == 0 && H <= 4 * 4 * 1024 &&
+      (((uintptr_t)residual | (uintptr_t)weight) & 15) == 0 && (((uintptr_t)delta | (uintptr_t)out) & 7) == 0) {
+    // whole rows in registers: one read of the residual, vector loads and stores
+    const int pieces = H / 4;
+    int block = 32;
+    while (block < 1024 && block < pieces) block <<= 1;
+    const int per_thread = (pieces + block - 1) / block;
+    if (per_thread <= 1)
+      launch_pdl(add_rmsnorm_vec_kernel<1>, dim3(R), dim3(block), 0, stream, residual, (const bf16*)delta, weight, eps,
+                 (bf16*)out, rows, H, unit_offset);
+    else if (per_thread <= 2)
+      launch_pdl(add_rmsnorm_vec_kernel<2>, dim3(R), dim3(block), 0, stream, residual, (const bf16*)delta, weight, eps,
+                 (bf16*)out, rows, H, unit_offset);
+    else
+      launch_pdl(add_rmsnorm_vec_kernel<4>, dim3(R), dim3(block), 0, stream, residual, (const bf16*)delta, weight, eps,
+                 (bf16*)out, rows, H, unit_offset);
+    return launched();
+  }
   SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(add_rmsnorm_kernel<TA>, dim3(R), dim3(norm_block(H)), 0, stream,
       residual, (const TA*)delta, weight, eps, (TA*)out, rows, H, unit_offset));
   return launched();

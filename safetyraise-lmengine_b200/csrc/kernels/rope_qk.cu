@@ -83,6 +83,66 @@ __global__ void qk_norm_rope_append_kernel(
   for (int d = 2 * rotary_half + lane; d < hd; d += 32) put(d, get(d));   // unrotated tail
 }
 
+// The same for bfloat16 with head_dim = 32 * EPL and a rotation over the whole head (rotary_half =
+// head_dim / 2): a lane holds EPL consecutive elements in one vector load, the partner of a pair
+// (i, i + head_dim / 2) sits in lane ^ 16, and every row is read and written once in whole sectors.
+template <int EPL>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_append_vec_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                               bf16* __restrict__ v_cache, const float* __restrict__ q_norm_w,
+                               const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
+                               const float* __restrict__ sin_t, const int* __restrict__ kv_slot, int T, int nq,
+                               int nkv, int heads_total, int write_kv, int page_size) {
+  constexpr int HD = 32 * EPL, HALF = HD / 2;
+  struct alignas(2 * EPL) Vec { bf16 v[EPL]; };
+  pdl_wait();
+  pdl_trigger();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T * heads_total) return;
+  const int t = warp / heads_total, head = warp % heads_total;
+  const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+  if (!is_q && !write_kv) return;
+  const int slot = is_q ? 0 : kv_slot[t];
+  if (!is_q && slot < 0) return;
+  const Vec raw = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads_total + head) * HD + lane * EPL);
+  bf16* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * nq + head) * HD;
+  } else {
+    const int kvh = is_k ? head - nq : head - nq - nkv;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * HD;
+  }
+  if (!is_q && !is_k) {   // value: copy
+    *reinterpret_cast<Vec*>(dst + lane * EPL) = raw;
+    return;
+  }
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  float x[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) x[j] = __bfloat162float(raw.v[j]);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) ss += x[j] * x[j];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) x[j] = x[j] * inv * w[lane * EPL + j];
+  }
+  // lanes 0..15 hold the left elements i of the pairs, lanes 16..31 the right elements i + HALF
+  const bool left = lane < 16;
+  const int i0 = (lane & 15) * EPL;
+  Vec out;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+    const float c = cos_t[(size_t)t * HALF + i0 + j], sn = sin_t[(size_t)t * HALF + i0 + j];
+    out.v[j] = __float2bfloat16_rn(left ? x[j] * c - other * sn : x[j] * c + other * sn);
+  }
+  *reinterpret_cast<Vec*>(dst + lane * EPL) = out;
+}
+
 }  // namespace srlm
 
 using namespace srlm;
@@ -113,6 +173,17 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
                   cache_dtype, act_dtype);
   const int heads_total = nq + 2 * nkv;
   const long long warps = (long long)T * heads_total;
+  if (act_dtype == DT_BF16 && 2 * rotary_half == hd && (hd == 64 || hd == 128 || hd == 256) &&
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
+    const long long grid = (warps * 32 + 255) / 256;
+#define SRLM_ROPE_VEC(EPL)                                                                                        \
+    launch_pdl(qk_norm_rope_append_vec_kernel<EPL>, dim3((unsigned)grid), dim3(256), 0, stream, (const bf16*)qkv,  \
+               (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t, kv_slot, T, nq,  \
+               nkv, heads_total, write_kv, page_size)
+    if (hd == 64) SRLM_ROPE_VEC(2); else if (hd == 128) SRLM_ROPE_VEC(4); else SRLM_ROPE_VEC(8);
+#undef SRLM_ROPE_VEC
+    return launched();
+  }
   const int block = 128;
   const long long grid = (warps * 32 + block - 1) / block;
   SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(qk_norm_rope_append_kernel<TA, TA>, dim3((unsigned)grid), dim3(block), 0, stream,
