@@ -202,6 +202,45 @@ def test_one_block_at_large_layer_sizes(size, dtype, tmp_path_factory):
     check_against_plain(got, folder, {"a": a, "b": b}, dtype)
 
 
+@pytest.fixture(scope="module")
+def long_prompt_folder(tmp_path_factory):
+    from conftest import make_folder
+    cfg = dict(TINY["B"][0], num_hidden_layers=2, hidden_size=256, num_attention_heads=8, num_key_value_heads=2,
+               head_dim=128, intermediate_size=384, vocab_size=512, max_position_embeddings=4096)
+    return make_folder(tmp_path_factory, cfg, 9, "long_prompt")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_in_portions_then_decoding(dtype, long_prompt_folder):
+    """3,000 tokens with heads of 128 (the tensor-memory attention kernel in bfloat16): portions of 1,024
+    whose keys span dozens of tiles and hundreds of pages, logits at the portions' ends, then decoding
+    beside the portion of another request."""
+    from safetyraise_lmengine_b200 import Engine
+    folder = long_prompt_folder
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=16, num_pages=220, max_requests=2,
+                             max_batch_tokens=1100, max_context=4096)
+    rng = np.random.default_rng(3)
+    a, b = random_tokens(rng, 3000, 512), random_tokens(rng, 40, 512)
+    steps, at = [], 0
+    for n in (1024, 1024, 940):                      # the last 8 places of every portion
+        steps.append({"entries": [("a", a[at:at + n], list(range(n - 8, n)))]})
+        at += n
+    steps.append({"entries": [("a", a[at:at + 1], [0]), ("b", b[:30], [28, 29])]})
+    at += 1
+    for i in range(10):
+        steps.append({"entries": [("a", a[at + i:at + i + 1], [0]), ("b", b[30 + i:31 + i], [0])]})
+    steps.append({"entries": [("a", a[at + 10:], [0])]})
+    got = replay(eng, steps)
+    assert len(got) == 3 * 8 + 1 + 2 + 20 + 1
+    ref_a, ref_b = plain_logits(folder, a), plain_logits(folder, b)
+    worst = 0.0
+    for (rid, pos), row in got.items():
+        ref = (ref_a if rid == "a" else ref_b)[pos]
+        worst = max(worst, np.abs(row - ref).max() / np.abs(ref).max())
+    assert worst <= TOL[dtype], worst
+    assert eng.cache.audit() == 0
+
+
 def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
     """Decode steps of up to 8 tokens run their RMSNorms inside the products around them; the same
     steps with the fusion switched off must give the same logits within rounding."""
