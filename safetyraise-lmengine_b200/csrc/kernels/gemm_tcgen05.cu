@@ -694,21 +694,15 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   const CUtensorMap* mw = cached_map(W, N, K, ldw, BM, true);
   const CUtensorMap* mx = cached_map(X, M, K, ldx, bn, false);
   if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
-  if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel
+  if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel (SRLM_GEMM_PERSISTENT=0: one tile per block)
     static const bool off = getenv("SRLM_GEMM_PERSISTENT") && !atoi(getenv("SRLM_GEMM_PERSISTENT"));
     if (!off) return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, stream) : launch_persistent<256, 4>(mw, mx, a, stream);
   }
   switch (bn) {
-    // few stages per block so that three (two at 128 tokens) blocks share an SM: their prologues and
-    // epilogues overlap one another's streaming, and tile counts that are no multiple of 148 still
-    // keep every SM busy; the bytes in flight per SM stay the same
-    case 16: {
-      static const int st16 = getenv("SRLM_GEMM_STAGES16") ? atoi(getenv("SRLM_GEMM_STAGES16")) : 4;
-      if (st16 == 2) return launch<16, 2>(mw, mx, a, splits, stream);
-      if (st16 == 8) return launch<16, 8>(mw, mx, a, splits, stream);
-      if (st16 == 12) return launch<16, 12>(mw, mx, a, splits, stream);
-      return launch<16, 4>(mw, mx, a, splits, stream);
-    }
+    // stages chosen so that two or three blocks share an SM: their prologues and epilogues overlap one
+    // another's streaming, and tile counts that are no multiple of 148 still keep every SM busy; at
+    // 17..64 tokens a block's stream is bound by the latency of its ring, hence the deeper rings there
+    case 16: return launch<16, 4>(mw, mx, a, splits, stream);
     case 32: return launch<32, 5>(mw, mx, a, splits, stream);
     case 64: return launch<64, 4>(mw, mx, a, splits, stream);
     case 128: return launch<128, 3>(mw, mx, a, splits, stream);
