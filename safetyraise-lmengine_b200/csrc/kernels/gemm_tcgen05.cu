@@ -165,7 +165,7 @@ struct GemmArgs {
   long long ldc;
   int* err_flag;
   int kb_per_split;        // k blocks each split handles
-  float* partial;          // [splits, tiles, 128, BN] float32 (split-K only)
+  float* partial;          // [splits, tiles, BN tokens, 128] float32 (split-K only)
   int* tile_counters;      // one per output tile, zero on entry (split-K only)
   int swiglu8;             // 1: weight rows come in blocks of 16 (8 gate rows, then the 8 up rows of the same
                            //    features); the output is silu(gate) * up, [M, N/2]
@@ -290,42 +290,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     __syncwarp();
   } else {
+    // ---------------- epilogue: four warps ----------------
+    // The accumulator D[weight row n, token m] leaves TMEM one weight row per thread; it is turned
+    // through shared memory (the ring is free once the accumulator is complete) so that everything
+    // behind it -- the rows of C, the partial sums of a K split -- moves as whole 16-byte pieces with
+    // the lanes of a warp side by side: thread (warp ew, lane) then owns the tokens ew, ew + 4, ...
+    // and the four weight rows 4 * lane .. 4 * lane + 3 of each.
     pdl_wait();
     const bool ok = mbar_wait(accum_bar, 0, args.err_flag, 3);
     tcgen05_fence_after();
-    const int lane_base = 32 * (warp & 3);              // the TMEM lanes this warp may read
-    const int n = n0 + lane_base + lane;
+    const int ew = warp & 3;
+    const int lane_base = 32 * ew;                      // the TMEM lanes this warp may read
     constexpr int CH = BN < 32 ? 16 : 32;
+    constexpr int SROW = BM + 4;                        // floats per token row of the slab (padded)
+    static_assert(BN * SROW * 4 <= STAGES * STAGE, "the epilogue's slab lives in the ring");
+    float* slab = reinterpret_cast<float*>(smem);      // [BN tokens][SROW]
     const bool split = gridDim.z > 1;
-    // split-K: the partial sums of a tile lie as [split][tile][128 weight rows][BN tokens], so a thread
-    // (one weight row) writes and reads its tokens as whole 16-byte pieces
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const size_t tile_floats = (size_t)BM * BN;
-    float* mine = split ? args.partial + ((size_t)blockIdx.z * gridDim.x * gridDim.y + tile) * tile_floats +
-                              (size_t)(lane_base + lane) * BN
-                        : nullptr;
+    const int rows = min(BN, args.M - m0);
     if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
         uint32_t v[CH];
         tmem_load<CH>(tmem_base + ((uint32_t)lane_base << 16) + c, v);
         tmem_load_wait();
-        if (split) {
 #pragma unroll
-          for (int j = 0; j < CH; j += 4)
-            *reinterpret_cast<uint4*>(mine + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int m = m0 + c + j;
-            if (m < args.M) store_result(args, m, n, __uint_as_float(v[j]), n < args.N);      // the same m for every lane
-          }
-        }
+        for (int j = 0; j < CH; ++j) slab[(c + j) * SROW + lane_base + lane] = __uint_as_float(v[j]);
       }
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    bool finish = ok;
     if (split) {
-      // the last split to finish this tile adds the partials in split order (the same order on
-      // every run) and writes the result
+      // this split's sums go out as [split][tile][token][128 weight rows]; the split that arrives last
+      // adds all of them in split order (the same order on every run) and writes the result
+      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+      const size_t tile_floats = (size_t)BN * BM;
+      const size_t split_floats = (size_t)gridDim.x * gridDim.y * tile_floats;
+      float* mine = args.partial + blockIdx.z * split_floats + (size_t)tile * tile_floats;
+      for (int m = ew; m < rows; m += 4)
+        *reinterpret_cast<float4*>(mine + (size_t)m * BM + 4 * lane) =
+            *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
@@ -334,42 +337,91 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (*last_flag) args.tile_counters[tile] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag) {
+      finish = *last_flag != 0;
+      if (finish) {
         __threadfence();
-        const int rows = min(BN, args.M - m0), nz = (int)gridDim.z;
-        const size_t split_floats = (size_t)gridDim.x * gridDim.y * tile_floats;
-        const bool have = n < args.N;
-        // 16 tokens at a time, four splits at a time: one trip to L2 with sixteen 16-byte loads in
-        // flight per thread (the loads are gathered first: folded into the additions they would be
-        // issued one behind the other); the additions run in split order
-        constexpr int RB = 16, ZB = 4;
-        const float* first = args.partial + (size_t)tile * tile_floats + (size_t)(lane_base + lane) * BN;
-        for (int j = 0; j < rows; j += RB) {
-          float x[RB];
+        const int nz = (int)gridDim.z;
+        const float* first = args.partial + (size_t)tile * tile_floats + 4 * lane;
+        // four tokens at a time, so that 4 x nz loads are in flight per thread
+        for (int m = ew; m < rows; m += 16) {
+          float4 x[4];
 #pragma unroll
-          for (int u = 0; u < RB; ++u) x[u] = 0.f;
-          for (int z0 = 0; z0 < nz; z0 += ZB) {
-            float4 t[ZB][RB / 4];
+          for (int u = 0; u < 4; ++u) x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int z = 0; z < nz; ++z) {
+            float4 t[4];
 #pragma unroll
-            for (int zz = 0; zz < ZB; ++zz) {
-              const float* src = first + j + (size_t)min(z0 + zz, nz - 1) * split_floats;
-#pragma unroll
-              for (int u = 0; u < RB / 4; ++u) t[zz][u] = __ldcg(reinterpret_cast<const float4*>(src) + u);
+            for (int u = 0; u < 4; ++u) {
+              const int mm = min(m + 4 * u, rows - 1);
+              t[u] = __ldcg(reinterpret_cast<const float4*>(first + z * split_floats + (size_t)mm * BM));
             }
 #pragma unroll
-            for (int zz = 0; zz < ZB; ++zz) {
-              if (z0 + zz < nz) {
+            for (int u = 0; u < 4; ++u) { x[u].x += t[u].x; x[u].y += t[u].y; x[u].z += t[u].z; x[u].w += t[u].w; }
+          }
 #pragma unroll
-                for (int u = 0; u < RB / 4; ++u) {
-                  x[4 * u] += t[zz][u].x; x[4 * u + 1] += t[zz][u].y;
-                  x[4 * u + 2] += t[zz][u].z; x[4 * u + 3] += t[zz][u].w;
-                }
+          for (int u = 0; u < 4; ++u)
+            if (m + 4 * u < rows) *reinterpret_cast<float4*>(slab + (m + 4 * u) * SROW + 4 * lane) = x[u];
+        }
+      }
+      // each thread reads back below what it wrote itself: no barrier needed, except for SwiGLU (the
+      // up rows sit in another lane's columns)
+      if (finish && args.swiglu8) __syncwarp();
+    }
+    if (finish) {
+      // rows of the slab -> C
+      const int esize = args.c_is_f32 ? 4 : 2;
+      const bool vec_ok = (args.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
+      if (args.swiglu8) {
+        // the 16 rows 16 b .. 16 b + 15 are 8 gate rows and the 8 up rows of the same features:
+        // lanes with lane % 4 < 2 hold gate rows, the up rows are two lanes further
+        if ((lane & 3) < 2) {
+          const int col = (n0 >> 1) + (lane >> 2) * 8 + (lane & 1) * 4;       // first of 4 columns of C
+          const int width = args.N >> 1;
+          for (int m = ew; m < rows; m += 4) {
+            const float4 g = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
+            const float4 u = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane + 8);
+            const float h[4] = {silu_stable(g.x) * u.x, silu_stable(g.y) * u.y, silu_stable(g.z) * u.z,
+                                silu_stable(g.w) * u.w};
+            uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + m) * args.ldc + col) * esize;
+            if (vec_ok && col + 4 <= width) {
+              if (args.c_is_f32) {
+                *reinterpret_cast<float4*>(dst) = make_float4(h[0], h[1], h[2], h[3]);
+              } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(h[0], h[1]), hi = __floats2bfloat162_rn(h[2], h[3]);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = pk;
+              }
+            } else {
+              for (int e = 0; e < 4 && col + e < width; ++e) {
+                if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = h[e];
+                else reinterpret_cast<bf16*>(dst)[e] = __float2bfloat16_rn(h[e]);
               }
             }
           }
-#pragma unroll
-          for (int u = 0; u < RB; ++u)
-            if (j + u < rows) store_result(args, m0 + j + u, n, x[u], have);
+        }
+      } else {
+        const int col = n0 + 4 * lane;
+        for (int m = ew; m < rows; m += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
+          const float h[4] = {x.x, x.y, x.z, x.w};
+          uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + m) * args.ldc + col) * esize;
+          if (vec_ok && col + 4 <= args.N) {
+            if (args.c_is_f32) {
+              *reinterpret_cast<float4*>(dst) = x;
+            } else {
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(h[0], h[1]), hi = __floats2bfloat162_rn(h[2], h[3]);
+              uint2 pk;
+              pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+              pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(dst) = pk;
+            }
+          } else {
+            for (int e = 0; e < 4 && col + e < args.N; ++e) {
+              if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = h[e];
+              else reinterpret_cast<bf16*>(dst)[e] = __float2bfloat16_rn(h[e]);
+            }
+          }
         }
       }
     }
@@ -661,7 +713,7 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
 using namespace srlm;
 
 // workspace (only when splits > 1): one int per output tile, zero on entry and left zero on exit,
-// at the start; float32 partials [splits, tiles, 128, token tile] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
+// at the start; float32 partials [splits, tiles, token tile, 128] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
 extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                     long long ldx, long long ldw, long long ldc, int splits, void* workspace,
                                     long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
@@ -760,7 +812,7 @@ extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C
   splits = (total_kb + kb_per_split - 1) / kb_per_split;
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
-  const long long need = 65536 + (long long)splits * M * N * 4;
+  const long long need = 65536 + (long long)splits * tiles * BM * bn * 4;      // partial sums lie in whole tiles
   if (splits > 1 && (need > SRLM_STATIC_SCRATCH_BYTES || tiles * 4 > 65536))
     return refuse(ST_BAD_SIZE, "gemm_static: %d splits of a %d x %d product need %lld bytes of scratch, the "
                   "built-in array holds %d; use fewer splits or the entry point that takes a workspace",

@@ -181,14 +181,12 @@ class KernelLibrary:
         if tiles >= 1024 or M > 256:
             return 1
         if M > 16:
-            # measured on B200 inside decode steps: up to 32 tokens, splitting until about 148 blocks
-            # stream at once pays (batch 32: 7.9 -> 6.9 ms a step); up to 64 tokens it pays only for a
-            # long K with few tiles (the down projection); beyond that the partial sums cost more than
-            # the idle SMs
-            if M <= 32:
-                sp = max(1, min(148 // max(1, tiles), total_kb // 8))
-            elif M <= 64 and total_kb >= 128 and tiles < 64:
-                sp = 4
+            # measured on B200 inside decode steps: up to 64 tokens, splitting until about one block per
+            # SM streams (a few more up to 32 tokens) pays (batch 32: 7.9 -> 5.9 ms a step, batch 64:
+            # 9.8 -> 8.5 ms), each split keeping at least 8 k-blocks; beyond 64 tokens the persistent
+            # kernel without a split is faster
+            if M <= 64:
+                sp = max(1, min((222 if M <= 32 else 148) // max(1, tiles), total_kb // 8))
             else:
                 sp = 1
             while sp > 1 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
