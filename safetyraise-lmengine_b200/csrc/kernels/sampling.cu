@@ -6,6 +6,29 @@
 
 namespace srlm {
 
+// Calls f(i, row[i]) for this thread's share of a row, every index once, in ascending order per thread.
+// Rows of a multiple of 4 floats on a 16-byte boundary are read as float4, two loads in flight.
+template <typename F>
+__device__ __forceinline__ void for_each_of_row(const float* __restrict__ row, int V, F f) {
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2, step = blockDim.x;
+    for (int j = threadIdx.x; j < n4; j += 2 * step) {
+      const float4 a = row4[j];
+      const bool more = j + step < n4;
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (more) b = row4[j + step];
+      f(4 * j, a.x); f(4 * j + 1, a.y); f(4 * j + 2, a.z); f(4 * j + 3, a.w);
+      if (more) {
+        const int i = 4 * (j + step);
+        f(i, b.x); f(i + 1, b.y); f(i + 2, b.z); f(i + 3, b.w);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+  }
+}
+
 // One block per row.  out_token[row] = argmax; bad[0] set if a logit is not finite.
 __global__ void argmax_kernel(const float* __restrict__ logits, long long row_stride, int V,
                               int* __restrict__ out_token, int* __restrict__ bad) {
@@ -15,11 +38,10 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long row_st
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
   bool nonfinite = false;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
+  for_each_of_row(row, V, [&](int i, float v) {
     if (!isfinite(v)) nonfinite = true;
-    if (v > bv) { bv = v; bi = i; }          // strided scan: ascending i per thread
-  }
+    if (v > bv) { bv = v; bi = i; }          // ascending i per thread: the first of equal values stays
+  });
   if (nonfinite) atomicExch(bad, 1);
   auto better = [](float v1, int i1, float v2, int i2) { return v1 > v2 || (v1 == v2 && i1 < i2); };
 #pragma unroll
@@ -65,32 +87,33 @@ extern "C" int srlm_argmax(const float* logits, long long row_stride, int n, int
 //   value descending and id ascending -> keep top_k -> softmax over the kept ->
 //   keep the shortest prefix whose mass >= top_p -> draw = u * kept mass ->
 //   first element whose running mass reaches the draw.
-// Nothing is sorted.  "The element at which a running total in sorted order
-// reaches a target" is found by bisection on the 32 bits of the order key:
-// each probe is one pass over the row and a block sum in a fixed order, so the
-// result is the same on every run.  Equal keys are ordered by id with a second
-// bisection on the id, taken only when a tie sits on a boundary.
+// Nothing is sorted.  The adjusted values are written once to a scratch row; "the
+// element at which a running total in sorted order reaches a target" is then found
+// by a radix search over the 32 bits of the order key, 8 bits a pass: a pass adds
+// the elements that match the prefix found so far into 256 bins, and a scan of the
+// bins from the top gives the next 8 bits.  Counts (top-k) and masses are integers
+// (a mass is exp(v - max) in units of 2^-31), so the sums do not depend on the
+// order of the additions: the same token on every run.  Elements with equal keys
+// are ordered by id; a tie on a boundary is resolved by a search over the ids.
+// About a dozen passes over the row instead of a hundred.
 // ---------------------------------------------------------------------------
 namespace srlm {
+
+typedef unsigned long long u64;
 
 __device__ __forceinline__ uint32_t order_key(float v) {   // larger value -> larger key
   const uint32_t b = __float_as_uint(v);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-
-struct RowView {
-  const float* logits;
-  const uint32_t* seen;     // bitmap of history ids in shared memory, or nullptr
-  float penalty, inv_temperature_unused, temperature;
-  int V;
-  __device__ __forceinline__ float value(int i) const {
-    float x = logits[i];
-    if (seen && (seen[i >> 5] >> (i & 31) & 1u)) x = x < 0.f ? x * penalty : x / penalty;
-    return temperature > 0.f ? x / temperature : x;
-  }
-};
-
-__device__ __forceinline__ float block_sum_f(float v, float* scratch) { return block_sum(v, scratch); }
+__device__ __forceinline__ float key_value(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+// exp(v - vmax) in units of 2^-31: 2^31 for the maximum, 0 below about 2^-31 of it
+__device__ __forceinline__ uint32_t mass_of(float v, float vmax) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((v - vmax) * 1.4426950408889634f));
+  return (uint32_t)(e * 2147483648.0f);
+}
 
 __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -115,141 +138,145 @@ struct Kept {
   }
 };
 
-// mass(i) of element i, zero outside the kept set.
-struct Mass {
-  RowView row;
-  Kept kept;
-  float vmax, total;
-  __device__ __forceinline__ float of(int i, uint32_t* key_out) const {
-    const float v = row.value(i);
-    const uint32_t key = order_key(v);
-    *key_out = key;
-    return kept.has(key, i) ? expf(v - vmax) / total : 0.f;
-  }
+constexpr int REPLICAS = 32;          // one copy of the bins per lane: the lanes of a warp never meet
+constexpr int REPLICA_STRIDE = 257;   // in bins: the copies of a bin fall on different banks
+
+struct Shared {
+  u64 bins[256];          // the pass in progress (the copies added up)
+  u64 first[256];         // masses of the kept set by the top 8 bits of the key (reused by both searches)
+  u64 found[3];           // digit, sum above it, its own bin
+  int low_id[256];        // smallest id that fell into each bin of the last pass (kept for shift == 0)
+  int is[32];
+  int id_lo, id_hi;
 };
 
-// Running mass in sorted order reaches `target` at element (key*, id*): returns them and the mass
-// up to and including that element.  If the whole mass stays below target, returns the last
-// element of the kept set (smallest kept key, largest id).
-__device__ void select_by_mass(const Mass& m, float target, float* fs, int* is, uint32_t* key_sel,
-                               int* id_sel, float* mass_through) {
-  const int V = m.row.V;
-  // largest key k with  sum_{key >= k} mass >= target
-  uint32_t lo = 0, hi = 0xffffffffu;      // invariant: G(lo) >= target (or lo == 0), G(hi+1) < target
-  bool any = false;
-  for (int bit = 31; bit >= 0; --bit) {
-    const uint32_t probe = lo | (1u << bit);
-    float part = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      uint32_t key;
-      const float w = m.of(i, &key);
-      if (key >= probe) part += w;
-    }
-    const float g = block_sum_f(part, fs);
-    if (g >= target) { lo = probe; any = true; }
-  }
-  (void)hi;
-  __shared__ uint32_t s_min_key;
-  if (!any) {
-    // even the whole kept mass is below the target (rounding, e.g. top_p = 1): the last kept
-    // element, i.e. the smallest kept key and among its holders the largest id
-    if (threadIdx.x == 0) s_min_key = 0xffffffffu;
+// One radix pass: adds `weight(v)` of every element for which `match(key, i)` holds into the bin of its
+// digit at `shift`, then scans the bins from the top: the digit at which `above + bins` first reaches
+// `target`, the sum above that digit, and the digit's own bin go to sh.found.  The keys of a row share
+// few leading digits, so every lane adds into a copy of the bins of its own (`copies`, in dynamic shared
+// memory); the copies are summed before the scan.  Integer additions: any order gives the same sums.
+template <typename Match, typename Weight>
+__device__ __forceinline__ void radix_pass(const float* v, int V, int shift, u64 above, u64 target, Shared& sh,
+                                           u64* copies, Match match, Weight weight, bool fill) {
+  if (fill) {
+    for (int i = threadIdx.x; i < REPLICAS * REPLICA_STRIDE; i += blockDim.x) copies[i] = 0;
+    if (shift == 0)
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) sh.low_id[i] = 0x7fffffff;
     __syncthreads();
-    uint32_t local = 0xffffffffu;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const uint32_t key = order_key(m.row.value(i));
-      if (m.kept.has(key, i)) local = min(local, key);
-    }
-    atomicMin(&s_min_key, local);
-    __syncthreads();
-    lo = s_min_key;
-  }
-  // mass strictly above lo, and how many elements share the key lo
-  float above_p = 0.f;
-  int ties_p = 0, min_id = 0x7fffffff, max_id = -1;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    uint32_t key;
-    const float w = m.of(i, &key);
-    if (key > lo) above_p += w;
-    if (key == lo && m.kept.has(key, i)) { ties_p += 1; min_id = min(min_id, i); max_id = max(max_id, i); }
-  }
-  const float above = block_sum_f(above_p, fs);
-  const int ties = block_sum_i(ties_p, is);
-  // min / max id over the block
-  __shared__ int s_min, s_max;
-  if (threadIdx.x == 0) { s_min = 0x7fffffff; s_max = -1; }
-  __syncthreads();
-  if (ties_p) { atomicMin(&s_min, min_id); atomicMax(&s_max, max_id); }
-  __syncthreads();
-  int pick = s_min;
-  float through;
-  if (ties <= 1 || !any) {
-    if (!any) pick = s_max;
-    float part = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      uint32_t key;
-      const float w = m.of(i, &key);
-      if (key == lo && i <= pick) part += w;
-    }
-    through = above + block_sum_f(part, fs);
-  } else {
-    // smallest id c with above + sum_{key == lo, id <= c} mass >= target
-    int a = s_min, b = s_max;
-    while (a < b) {
-      const int mid = a + (b - a) / 2;
-      float part = 0.f;
-      for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        uint32_t key;
-        const float w = m.of(i, &key);
-        if (key == lo && i <= mid) part += w;
+    u64* mine = copies + (threadIdx.x & (REPLICAS - 1)) * REPLICA_STRIDE;
+    for_each_of_row(v, V, [&](int i, float x) {
+      const uint32_t key = order_key(x);
+      if (match(key, i)) {
+        const u64 w = weight(x);
+        const uint32_t d = (key >> shift) & 255u;
+        if (w) atomicAdd(&mine[d], w);
+        if (shift == 0) atomicMin(&sh.low_id[d], i);
       }
-      if (above + block_sum_f(part, fs) >= target) b = mid; else a = mid + 1;
+    });
+    __syncthreads();
+    for (int d = threadIdx.x; d < 256; d += blockDim.x) {
+      u64 sum = 0;
+#pragma unroll 8
+      for (int c = 0; c < REPLICAS; ++c) sum += copies[c * REPLICA_STRIDE + d];
+      sh.bins[d] = sum;
     }
-    // a may fall between ids that hold the key; move it to the holder at or below... the smallest
-    // holder >= a that satisfies the bound is a itself or the next holder; find the smallest holder >= a
     __syncthreads();
-    if (threadIdx.x == 0) s_min = 0x7fffffff;
-    __syncthreads();
-    int local = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x)
-      if (i >= a && order_key(m.row.value(i)) == lo && m.kept.has(lo, i)) { local = i; break; }
-    if (local != 0x7fffffff) atomicMin(&s_min, local);
-    __syncthreads();
-    pick = s_min == 0x7fffffff ? s_max : s_min;
-    float part = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      uint32_t key;
-      const float w = m.of(i, &key);
-      if (key == lo && i <= pick) part += w;
+  }
+  if (threadIdx.x == 0) {
+    u64 acc = above;
+    int d = 255;
+    for (; d > 0; --d) {
+      if (acc + sh.bins[d] >= target) break;
+      acc += sh.bins[d];
     }
-    through = above + block_sum_f(part, fs);
+    sh.found[0] = (u64)d;
+    sh.found[1] = acc;
+    sh.found[2] = sh.bins[d];
   }
   __syncthreads();
-  *key_sel = lo;
-  *id_sel = pick;
-  *mass_through = through;
+}
+
+// The n-th (1-based) smallest id among the elements of the kept set whose key is `key`.
+// `first_id`: the smallest such id if the caller knows it (the last radix pass records it), else -1.
+__device__ int nth_holder(const float* v, int V, uint32_t key, const Kept& kept, u64 n, u64 holders, int first_id,
+                          Shared& sh) {
+  if (n <= 1 && first_id >= 0) return first_id;
+  if (threadIdx.x == 0) { sh.id_lo = 0x7fffffff; sh.id_hi = -1; }
+  __syncthreads();
+  int lo = 0x7fffffff, hi = -1;
+  for_each_of_row(v, V, [&](int i, float x) {
+    if (order_key(x) == key && kept.has(key, i)) { lo = min(lo, i); hi = max(hi, i); }
+  });
+  if (hi >= 0) { atomicMin(&sh.id_lo, lo); atomicMax(&sh.id_hi, hi); }
+  __syncthreads();
+  int a = sh.id_lo, b = sh.id_hi;
+  __syncthreads();
+  if (n <= 1) return a;
+  if (n >= holders) return b;
+  while (a < b) {                         // smallest id c with #{holders with id <= c} >= n
+    const int mid = a + (b - a) / 2;
+    int part = 0;
+    for_each_of_row(v, V, [&](int i, float x) { part += (i <= mid && order_key(x) == key && kept.has(key, i)); });
+    if ((u64)block_sum_i(part, sh.is) >= n) b = mid; else a = mid + 1;
+  }
+  return a;
+}
+
+// The element of the kept set at which the running mass, in the order of key descending and id
+// ascending, first reaches `target` (1 <= target <= total mass).  sh.first must hold the kept set's
+// masses by the top 8 bits of the key.
+__device__ void select_by_mass(const float* v, int V, const Kept& kept, float vmax, u64 target, Shared& sh,
+                               u64* copies, uint32_t* key_sel, int* id_sel, u64* mass_through) {
+  uint32_t prefix = 0;
+  u64 above = 0;
+  for (int level = 0; level < 4; ++level) {
+    const int shift = 24 - 8 * level;
+    if (level == 0) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) sh.bins[i] = sh.first[i];
+      __syncthreads();
+    }
+    const uint32_t pre = prefix;
+    radix_pass(v, V, shift, above, target, sh, copies,
+               [&](uint32_t key, int i) { return kept.has(key, i) && (key >> (shift + 8)) == pre; },
+               [&](float x) { return (u64)mass_of(x, vmax); }, level != 0);
+    prefix = (prefix << 8) | (uint32_t)sh.found[0];
+    above = sh.found[1];
+  }
+  const u64 own = sh.found[2];                         // mass of the elements with this very key
+  const int first_id = sh.low_id[prefix & 255u];
+  __syncthreads();
+  const u64 w = (u64)mass_of(key_value(prefix), vmax);
+  const u64 holders = w ? own / w : 1;
+  u64 need = w ? (target > above ? (target - above + w - 1) / w : 1) : 1;
+  if (need < 1) need = 1;
+  if (need > holders) need = holders;
+  *key_sel = prefix;
+  *id_sel = nth_holder(v, V, prefix, kept, need, holders, first_id == 0x7fffffff ? -1 : first_id, sh);
+  *mass_through = above + need * w;
 }
 
 // One block per row.  hist_offsets[row]..hist_offsets[row+1] index `history` (ids for the penalty).
+// scratch: one row of V floats per row of logits.
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ penalty,
               const float* __restrict__ uniform, const int* __restrict__ history,
-              const int* __restrict__ hist_offsets, int* __restrict__ out_token, int* __restrict__ bad) {
-  extern __shared__ uint32_t seen_bits[];           // ceil(V / 32) words when a penalty applies
-  __shared__ float fs[32];
-  __shared__ int is[32];
+              const int* __restrict__ hist_offsets, float* __restrict__ scratch, int* __restrict__ out_token,
+              int* __restrict__ bad) {
+  extern __shared__ u64 dyn_smem[];                 // the copies of the bins, then the penalty's bitmap
+  u64* copies = dyn_smem;
+  uint32_t* seen_bits = reinterpret_cast<uint32_t*>(dyn_smem + REPLICAS * REPLICA_STRIDE);   // ceil(V / 32) words
+  __shared__ Shared sh;
   __shared__ float s_best_v[32];
   __shared__ int s_best_i[32];
   const int r = blockIdx.x;
-  RowView row;
-  row.logits = logits + (size_t)r * row_stride;
-  row.V = V;
-  row.temperature = temperature[r];
-  row.penalty = penalty ? penalty[r] : 1.f;
-  row.seen = nullptr;
-  if (row.penalty != 1.f && history) {
+  const float* row = logits + (size_t)r * row_stride;
+  float* v = scratch + (size_t)r * V;
+  const float temp = temperature[r];
+  const float pen = penalty ? penalty[r] : 1.f;
+  const bool use_pen = pen != 1.f && history;
+  if (use_pen) {
     const int words = (V + 31) >> 5;
     for (int i = threadIdx.x; i < words; i += blockDim.x) seen_bits[i] = 0u;
     __syncthreads();
@@ -258,17 +285,18 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
       if (tok >= 0 && tok < V) atomicOr(&seen_bits[tok >> 5], 1u << (tok & 31));
     }
     __syncthreads();
-    row.seen = seen_bits;
   }
-  // argmax of the adjusted values (ties to the lowest id) and the non-finite check
+  // the adjusted values, once; their argmax (ties to the lowest id) and the non-finite check
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
   bool nonfinite = false;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row.value(i);
-    if (!isfinite(row.logits[i])) nonfinite = true;
-    if (v > bv) { bv = v; bi = i; }
-  }
+  for_each_of_row(row, V, [&](int i, float x) {
+    if (!isfinite(x)) nonfinite = true;
+    if (use_pen && (seen_bits[i >> 5] >> (i & 31) & 1u)) x = x < 0.f ? x * pen : x / pen;
+    if (temp > 0.f) x = x / temp;
+    v[i] = x;
+    if (x > bv) { bv = x; bi = i; }
+  });
   if (nonfinite) atomicExch(bad, 1);
   auto better = [](float v1, int i1, float v2, int i2) { return v1 > v2 || (v1 == v2 && i1 < i2); };
 #pragma unroll
@@ -279,7 +307,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { s_best_v[warp] = bv; s_best_i[warp] = bi; }
-  __syncthreads();
+  __syncthreads();                                   // also: every thread's values are in the scratch row
   {
     const int nw = (blockDim.x + 31) >> 5;
     bv = lane < nw ? s_best_v[lane] : -CUDART_INF_F;
@@ -293,67 +321,61 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
   }
   // every thread of every warp now holds the row's best (value, id)
   if (bi == 0x7fffffff) bi = 0;
-  if (__syncthreads_or(nonfinite) || !(row.temperature > 0.f)) {
+  if (__syncthreads_or(nonfinite) || !(temp > 0.f)) {
     if (threadIdx.x == 0) out_token[r] = bi;
     return;
   }
-  // top-k: the k-th largest key, and the id cut among elements equal to it
+  // top-k: the k-th largest key, and the id cut among the elements equal to it
   Kept kept{0u, 0x7fffffff};
   const int k = top_k ? top_k[r] : 0;
   if (k > 0 && k < V) {
-    uint32_t lo = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-      const uint32_t probe = lo | (1u << bit);
-      int part = 0;
-      for (int i = threadIdx.x; i < V; i += blockDim.x) part += order_key(row.value(i)) >= probe;
-      if (block_sum_i(part, is) >= k) lo = probe;
+    uint32_t prefix = 0;
+    u64 above = 0;
+    for (int level = 0; level < 4; ++level) {
+      const int shift = 24 - 8 * level;
+      const uint32_t pre = prefix;
+      radix_pass(v, V, shift, above, (u64)k, sh, copies,
+                 [&](uint32_t key, int) { return level == 0 || (key >> (shift + 8)) == pre; },
+                 [](float) { return (u64)1; }, true);
+      prefix = (prefix << 8) | (uint32_t)sh.found[0];
+      above = sh.found[1];
     }
-    int above_p = 0, ties_p = 0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const uint32_t key = order_key(row.value(i));
-      above_p += key > lo;
-      ties_p += key == lo;
-    }
-    const int above = block_sum_i(above_p, is);
-    const int ties = block_sum_i(ties_p, is);
-    kept.kth = lo;
-    if (above + ties > k) {            // a tie on the boundary: keep the lowest ids among the equal
-      int a = 0, b = V - 1;
-      const int need = k - above;
-      while (a < b) {
-        const int mid = a + (b - a) / 2;
-        int part = 0;
-        for (int i = threadIdx.x; i < V; i += blockDim.x)
-          part += (i <= mid && order_key(row.value(i)) == lo);
-        if (block_sum_i(part, is) >= need) b = mid; else a = mid + 1;
-      }
-      kept.id_cut = a;
-    }
+    const u64 ties = sh.found[2];
+    const int first_id = sh.low_id[prefix & 255u];
+    __syncthreads();
+    kept.kth = prefix;
+    if (above + ties > (u64)k)             // a tie on the boundary: keep the lowest ids among the equal
+      kept.id_cut = nth_holder(v, V, prefix, Kept{0u, 0x7fffffff}, (u64)k - above, ties,
+                               first_id == 0x7fffffff ? -1 : first_id, sh);
   }
-  // softmax over the kept set
-  Mass m{row, kept, bv, 1.f};
-  float part = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    uint32_t key;
-    part += m.of(i, &key);
-  }
-  const float total = block_sum_f(part, fs);
-  if (!(total > 0.f) || !isfinite(total)) {
+  // the kept set's masses by the top 8 bits of the key; their sum is the softmax denominator
+  radix_pass(v, V, 24, 0, ~(u64)0, sh, copies, [&](uint32_t key, int i) { return kept.has(key, i); },
+             [&](float x) { return (u64)mass_of(x, bv); }, true);
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) sh.first[i] = sh.bins[i];
+  __syncthreads();
+  u64 total = 0;
+  for (int i = 0; i < 256; ++i) total += sh.first[i];
+  if (total == 0) {
     if (threadIdx.x == 0) { atomicExch(bad, 1); out_token[r] = bi; }
     return;
   }
-  m.total = total;
   // top-p cutoff: the shortest prefix whose mass >= top_p
-  uint32_t key_cut;
-  int id_cut;
-  float kept_mass;
-  select_by_mass(m, top_p[r], fs, is, &key_cut, &id_cut, &kept_mass);
+  const float tp = top_p[r];
+  uint32_t key_cut = 0;
+  int id_cut = 0x7fffffff;
+  u64 kept_mass = total;
+  if (tp < 1.f) {
+    u64 target = (u64)ceil((double)tp * (double)total);
+    target = target < 1 ? 1 : (target > total ? total : target);
+    select_by_mass(v, V, kept, bv, target, sh, copies, &key_cut, &id_cut, &kept_mass);
+  }
   // the draw
-  const float draw = uniform[r] * kept_mass;
+  u64 draw = (u64)ceil((double)uniform[r] * (double)kept_mass);
+  draw = draw < 1 ? 1 : (draw > kept_mass ? kept_mass : draw);
   uint32_t key_sel;
   int id_sel;
-  float through;
-  select_by_mass(m, draw, fs, is, &key_sel, &id_sel, &through);
+  u64 through;
+  select_by_mass(v, V, kept, bv, draw, sh, copies, &key_sel, &id_sel, &through);
   // never beyond the cutoff element (the reference falls back to the last kept element)
   if (key_sel < key_cut || (key_sel == key_cut && id_sel > id_cut)) id_sel = id_cut;
   if (threadIdx.x == 0) out_token[r] = id_sel;
@@ -361,20 +383,22 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
 
 }  // namespace srlm
 
+// scratch: n rows of V floats that the kernel may overwrite.
 extern "C" int srlm_sample(const float* logits, long long row_stride, int n, int V, const float* temperature,
                            const int* top_k, const float* top_p, const float* penalty, const float* uniform,
-                           const int* history, const int* hist_offsets, int* out_token, int* bad_flag,
-                           cudaStream_t stream) {
+                           const int* history, const int* hist_offsets, float* scratch, int* out_token,
+                           int* bad_flag, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (V <= 0 || row_stride < V) return refuse(ST_BAD_SIZE, "sample: V=%d stride=%lld", V, row_stride);
-  const size_t smem = history ? (size_t)((V + 31) / 32) * 4 : 0;
-  if (smem > 200 * 1024) return refuse(ST_BAD_SIZE, "sample: vocabulary %d is too large for the penalty bitmap", V);
+  if (!scratch) return refuse(ST_BAD_SIZE, "sample: a scratch row of V floats per row of logits is needed");
+  const size_t smem = (size_t)REPLICAS * REPLICA_STRIDE * 8 + (history ? (size_t)((V + 31) / 32) * 4 : 0);
+  if (smem > 190 * 1024) return refuse(ST_BAD_SIZE, "sample: vocabulary %d is too large for the penalty bitmap", V);
   static bool raised = false;
-  if (smem > 48 * 1024 && !raised) {
-    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (!raised) {
+    cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 190 * 1024);
     raised = true;
   }
   sample_kernel<<<n, 1024, smem, stream>>>(logits, row_stride, V, temperature, top_k, top_p, penalty, uniform,
-                                           history, hist_offsets, out_token, bad_flag);
+                                           history, hist_offsets, scratch, out_token, bad_flag);
   return launched();
 }

@@ -434,12 +434,15 @@ class KernelLibrary:
                                          _ptr(out_tokens), _ptr(bad_flag), _stream()), "argmax")
 
     def sample(self, logits, temperature, top_k, top_p, penalty, uniform, history, hist_offsets, out_tokens,
-               bad_flag):
+               bad_flag, scratch):
+        """scratch: float32 [n, V] that the kernel may overwrite (the adjusted values of each row)."""
         n, V = logits.shape
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < n * V:
+            raise ShapeError("sample: scratch must hold n x V float32 values")
         self._check(self.lib.srlm_sample(_ptr(logits), C.c_longlong(logits.stride(0)), C.c_int(n), C.c_int(V),
                                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty),
-                                         _ptr(uniform), _ptr(history), _ptr(hist_offsets), _ptr(out_tokens),
-                                         _ptr(bad_flag), _stream()), "sample")
+                                         _ptr(uniform), _ptr(history), _ptr(hist_offsets), _ptr(scratch),
+                                         _ptr(out_tokens), _ptr(bad_flag), _stream()), "sample")
 
 
 ops = KernelLibrary()

@@ -52,6 +52,7 @@ class Sampler:
         self._host = torch.empty(5 * rows, dtype=torch.float32, pin_memory=True)
         self._dev = torch.empty(5 * rows, dtype=torch.float32, device=self.device)
         self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        self._scratch = None               # [rows, vocab] float32, made when a row is first sampled
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
@@ -93,6 +94,8 @@ class Sampler:
                 offsets.append(len(flat))
             hist = torch.tensor(flat or [0], dtype=torch.int32, device=self.device)
             offs = torch.tensor(offsets, dtype=torch.int32, device=self.device)
+        if self._scratch is None or self._scratch.shape[0] < self._cap:
+            self._scratch = torch.empty(self._cap, self.vocab, dtype=torch.float32, device=self.device)
         ops.sample(logits, d[:n], d[4 * c:4 * c + n].view(torch.int32), d[c:c + n], d[2 * c:2 * c + n],
-                   d[3 * c:3 * c + n], hist, offs, self._out[:n], self.bad)
+                   d[3 * c:3 * c + n], hist, offs, self._out[:n], self.bad, self._scratch)
         return n
