@@ -53,6 +53,8 @@ class Sampler:
         self._dev = torch.empty(5 * rows, dtype=torch.float32, device=self.device)
         self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
         self._scratch = None               # [rows, vocab] float32, made when a row is first sampled
+        if not hasattr(self, "_hist_host"):
+            self._hist_host = self._hist_dev = None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int], histories: Sequence[Sequence[int]]) -> List[int]:
@@ -87,13 +89,28 @@ class Sampler:
         d = self._dev
         hist = offs = None
         if any(p.repetition_penalty != 1.0 for p in params):
-            offsets, flat = [0], []
-            for p, hh in zip(params, histories):
-                if p.repetition_penalty != 1.0:
-                    flat.extend(int(t) for t in hh)
-                offsets.append(len(flat))
-            hist = torch.tensor(flat or [0], dtype=torch.int32, device=self.device)
-            offs = torch.tensor(offsets, dtype=torch.int32, device=self.device)
+            # ids and row offsets go through one pinned buffer and one asynchronous copy: a pageable
+            # copy would make the host wait for the forward that is still running on the device
+            lens = [len(hh) if p.repetition_penalty != 1.0 else 0 for p, hh in zip(params, histories)]
+            total = sum(lens)
+            words = n + 1 + max(total, 1)
+            if self._hist_host is None or self._hist_host.numel() < words:
+                cap = max(words, 2 * (self._hist_host.numel() if self._hist_host is not None else 4096))
+                self._hist_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+                self._hist_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            hh_np = self._hist_host.numpy()
+            hh_np[0] = 0
+            np.cumsum(lens, out=hh_np[1:n + 1])
+            at = n + 1
+            for ln, hist_ids in zip(lens, histories):
+                if ln:
+                    hh_np[at:at + ln] = hist_ids
+                    at += ln
+            if total == 0:
+                hh_np[n + 1] = 0
+            self._hist_dev[:words].copy_(self._hist_host[:words], non_blocking=True)
+            offs = self._hist_dev[:n + 1]
+            hist = self._hist_dev[n + 1:words]
         if self._scratch is None or self._scratch.shape[0] < self._cap:
             self._scratch = torch.empty(self._cap, self.vocab, dtype=torch.float32, device=self.device)
         ops.sample(logits, d[:n], d[4 * c:4 * c + n].view(torch.int32), d[c:c + n], d[2 * c:2 * c + n],
