@@ -732,7 +732,9 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   if (splits > total_kb) splits = total_kb;
   int kb_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
-  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  // a few hundred tokens with a narrow output: token tiles of 256 would leave SMs without a tile
+  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < 148) bn = 128;
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0};
   if (splits > 1) {
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);

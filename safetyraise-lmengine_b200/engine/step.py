@@ -148,9 +148,10 @@ class Engine:
                 raise ShapeError(f"slot {e.slot} is not open")
             if start + n > self.max_context:
                 raise ShapeError(f"slot {e.slot}: {start}+{n} tokens exceed the context of {self.max_context}")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab and int(t) != LATER:
-                    raise ShapeError(f"token id {t} is outside the vocabulary of {vocab}")
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            wrong = ((ids < 0) | (ids >= vocab)) & (ids != LATER)
+            if wrong.any():
+                raise ShapeError(f"token id {int(ids[wrong][0])} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ShapeError(f"wanted place {w} is outside the entry's {n} tokens")
