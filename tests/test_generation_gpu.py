@@ -203,6 +203,39 @@ def test_sampling_kernel_follows_the_plain_sampler(V):
     assert again == got                               # same seed and index: same tokens
 
 
+@pytest.mark.parametrize("V, n", [(151936, 2), (40000, 30), (9000, 5), (8196, 70), (33000, 148)])
+def test_sampling_rows_shared_by_clusters_of_blocks(V, n):
+    """Long rows are shared by a cluster of 8, 4, 2 or 1 blocks, depending on their length and number:
+    every choice gives the plain sampler's token, and the argmax kernel the plain argmax."""
+    from safetyraise_lmengine_b200.kernels import ops
+    from safetyraise_lmengine_b200.sampling.params import SamplingParams
+    from safetyraise_lmengine_b200.sampling.sampler import Sampler, uniform_for
+    rng = np.random.default_rng(V + n)
+    rows = min(n, 12)                                   # rows checked against the plain sampler
+    logits = (rng.normal(0, 3.0, size=(n, V))).astype(np.float32)
+    logits[0, V - 3:] = 25.0                            # a tie at the top in the last block's slice
+    logits[1 % n, ::2] = logits[1 % n, 1::2][: (V + 1) // 2]   # many exact pairs of equal values
+    params, seeds, idx, hist = [], [], [], []
+    for i in range(n):
+        params.append(SamplingParams(temperature=[0.7, 1.0, 1.3][i % 3], top_p=[1.0, 0.9, 0.3][(i // 3) % 3],
+                                     top_k=[0, 2, 40, 3000][i % 4], repetition_penalty=[1.0, 1.2][i % 2]))
+        seeds.append(7 + i)
+        idx.append(i % 3)
+        hist.append([int(t) for t in rng.integers(0, V, size=20)] + [int(np.argmax(logits[i]))])
+    dev_logits = torch.tensor(logits, device=DEV)
+    s = Sampler(DEV, V, n)
+    got = s.sample(dev_logits, params, seeds, idx, hist)
+    assert s.bad.item() == 0 and len(got) == n
+    for i in range(rows):
+        p = params[i]
+        assert consistent_with_plain(got[i], logits[i], hist[i], p.temperature, p.top_k, p.top_p,
+                                     p.repetition_penalty, uniform_for(seeds[i], idx[i])), (i, got[i], vars(p))
+    assert s.sample(dev_logits, params, seeds, idx, hist) == got
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.argmax(dev_logits, out, s.bad)
+    assert out.tolist() == [int(np.argmax(r)) for r in logits]
+
+
 def test_sampling_statistics():
     """Frequencies over many draws follow the truncated distribution."""
     from safetyraise_lmengine_b200.sampling.params import SamplingParams
