@@ -5,12 +5,16 @@
 // thread walks the block table and brings whole pages in with tiled TMA copies
 // (a KV head's share of a page is one contiguous [page_size, head_dim] block of
 // the cache), 128-byte swizzled, into a ring of stages guarded by mbarriers.
-// Four consumer warps each compute the scores of all 64 keys of a tile
-// (mma.sync m16n8k16, float32 accumulation) and the online softmax, and each
-// accumulates one quarter of the head dimension of P.V, so nothing is merged
-// between warps.  Slices are merged by whichever block of an (entry, KV head)
-// finishes last, in slice order.  Every wait is bounded: when a bound is hit the
-// block raises the error flag and leaves.
+// Four consumer warps each take 16 of a tile's 64 keys through both products
+// (mma.sync m16n8k16, float32 accumulation) with a running maximum, sum and
+// output of their own; the four are merged once, in warp order, after the last
+// tile.  The slices of an (entry, KV head) are merged in slice order: when they
+// are at most 8, the blocks form a thread-block cluster and each adds a share of
+// the output elements out of the others' shared memory; otherwise through
+// partial results in global memory, by whichever block finishes last.  Every
+// wait is bounded: when a bound is hit the block raises the error flag and goes
+// on to the merge without waiting again, so every block of a cluster reaches
+// the cluster's barriers.
 //
 // Taken when head_dim is a multiple of 64 and page_size is 8, 16, 32 or a
 // multiple of 64; other sizes use the cp.async kernel in attention_mma.cu.
@@ -44,6 +48,8 @@ struct Args {
   float scale_log2;
   int window;
   int kv_chunk, nsplit;
+  int clustered;           // 1: the nsplit blocks of an (entry, KV head) form a thread-block cluster and merge
+                           //    their slices through distributed shared memory; 0: through part_o / part_ml
   float* part_o;
   float* part_ml;
   int* slice_counters;
@@ -117,6 +123,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void cluster_sync() {       // every thread of every block of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the float at `mine` (an address in this block's shared memory) in block `rank` of the cluster
+__device__ __forceinline__ float peer_f32(const float* mine, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(s32(mine)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // Address of the 16-byte chunk `chunk16` (of head_dim/8) of key `key` in a tile made of panels of
 // 64 dims: [panel][64 keys][128 bytes], 128-byte swizzle (chunk ^= key & 7).
 __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int key, int chunk16) {
@@ -135,7 +153,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   constexpr int KW = KT / CONSUMERS;                 // keys of a tile per consumer warp
   constexpr int OS = HD + 8;                         // row stride of the merge buffer, in floats
   static_assert(KW == 16, "a consumer warp takes one k-step of 16 keys per tile");
-  static_assert(CONSUMERS * 16 * (OS + 2) * 4 <= STAGES * 2 * TILE_BYTES, "the merge buffer lives in the tile memory");
+  static_assert((CONSUMERS * 16 * (OS + 2) + 16 * (HD + 2)) * 4 <= STAGES * 2 * TILE_BYTES,
+                "the merge buffers live in the tile memory");
   extern __shared__ uint8_t dec_smem_raw[];
   uint8_t* smem = dec_smem_raw + ((1024u - (s32(dec_smem_raw) & 1023u)) & 1023u);
   uint8_t* tiles = smem;                                              // [STAGES][K tile | V tile]
@@ -373,6 +392,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
       if (a.nsplit == 1) {
         a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+      } else if (a.clustered) {
+        float* blk_o = ml_s + CONSUMERS * 16 * 2;         // [16][HD], then [16][2]: this block's slice
+        blk_o[row * HD + d] = oo;
+        if (d == 0) { blk_o[16 * HD + row * 2] = mm; blk_o[16 * HD + row * 2 + 1] = ll; }
       } else {
         a.part_o[(slab * 16 + row) * HD + d] = oo;
         if (d == 0) *reinterpret_cast<float2*>(a.part_ml + (slab * 16 + row) * 2) = make_float2(mm, ll);
@@ -381,6 +404,30 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   const size_t slab0 = ((size_t)e * a.nkv + kvh) * a.nsplit;
   if (a.nsplit == 1) return;
+  if (a.clustered) {
+    // The slices of an (entry, KV head) sit in the shared memory of the cluster's blocks: block z adds
+    // the elements z, z + nsplit, ... of the output in slice order, reading the other blocks' memory.
+    // Every thread of every block passes both barriers (no path above returns before this point).
+    const float* blk_o = reinterpret_cast<const float*>(tiles) + CONSUMERS * 16 * (OS + 2);
+    const float* blk_ml = blk_o + 16 * HD;
+    cluster_sync();
+    const uint32_t n = (uint32_t)a.nsplit;
+    for (int idx = z * THREADS + threadIdx.x; idx < rows_total * HD; idx += (int)n * THREADS) {
+      const int row = idx / HD, d = idx - row * HD;
+      float mm = -CUDART_INF_F;
+      for (uint32_t sl = 0; sl < n; ++sl) mm = fmaxf(mm, peer_f32(blk_ml + row * 2, sl));
+      const float base = mm == -CUDART_INF_F ? 0.f : mm;
+      float ll = 0.f, oo = 0.f;
+      for (uint32_t sl = 0; sl < n; ++sl) {
+        const float f = exp2f(peer_f32(blk_ml + row * 2, sl) - base);
+        ll += peer_f32(blk_ml + row * 2 + 1, sl) * f;
+        oo += peer_f32(blk_o + row * HD + d, sl) * f;
+      }
+      a.out[((size_t)(q0 + row / g) * a.nq + kvh * g + row % g) * HD + d] = __float2bfloat16_rn(ll > 0.f ? oo / ll : 0.f);
+    }
+    cluster_sync();                       // nobody leaves while another block still reads its memory
+    return;
+  }
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -713,8 +760,27 @@ static int launch(const CUtensorMap* mk, const CUtensorMap* mv, const Args& a, i
     if (err != cudaSuccess) return refuse((int)err, "attention_decode_tma: cannot get %d bytes of shared memory", SMEM);
     configured = true;
   }
-  launch_pdl(attention_decode_tma_kernel<HD>, dim3(n_entries, a.nkv, a.nsplit), dim3(THREADS), SMEM, stream, *mk,
-             *mv, a);
+  if (!a.clustered) {
+    launch_pdl(attention_decode_tma_kernel<HD>, dim3(n_entries, a.nkv, a.nsplit), dim3(THREADS), SMEM, stream, *mk,
+               *mv, a);
+    return launched();
+  }
+  // the slices of an (entry, KV head) as one thread-block cluster along z
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_entries, a.nkv, a.nsplit);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = a.nsplit;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD>, *mk, *mv, a);
   return launched();
 }
 
@@ -750,11 +816,15 @@ extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cach
                                                const int* cu_q, const int* kv_lens, int n_entries, int nq, int nkv,
                                                int hd, int page_size, float scale, int window, int kv_chunk,
                                                int nsplit, float* part_o, float* part_ml, int* slice_counters,
-                                               int* err_flag, cudaStream_t stream) {
+                                               int cluster, int* err_flag, cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
   if (!srlm_attention_decode_tma_takes(hd, page_size) || nq <= 0 || nkv <= 0 || nq % nkv)
     return refuse(ST_BAD_SIZE, "attention_decode_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
-  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % dec::KT || (nsplit > 1 && (!part_o || !part_ml || !slice_counters)))
+  // up to 8 slices (the portable cluster size) can merge through distributed shared memory; more, or
+  // cluster == 0, go through part_o / part_ml and the counters
+  const int clustered = cluster && nsplit > 1 && nsplit <= 8;
+  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % dec::KT ||
+      (nsplit > 1 && !clustered && (!part_o || !part_ml || !slice_counters)))
     return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
   if (nsplit > 32 || nkv > 65535)
     return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d nkv=%d (at most 32 slices: the merge gives a lane to each)",
@@ -765,7 +835,8 @@ extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cach
   const CUtensorMap* mv = dec::cache_map(v_cache, rows, hd, box_rows);
   if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
   dec::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, nq, nkv, hd, page_size,
-              scale * 1.4426950408889634f, window, kv_chunk, nsplit, part_o, part_ml, slice_counters, err_flag};
+              scale * 1.4426950408889634f, window, kv_chunk, nsplit, clustered, part_o, part_ml, slice_counters,
+              err_flag};
   switch (hd) {
     case 64: return dec::launch<64>(mk, mv, a, n_entries, stream);
     case 128: return dec::launch<128>(mk, mv, a, n_entries, stream);

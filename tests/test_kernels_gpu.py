@@ -388,8 +388,10 @@ def test_mma_attention_finds_one_far_key(kernel):
 @pytest.mark.parametrize("nq, nkv, hd, ps", [(32, 8, 128, 16), (8, 2, 64, 16), (4, 4, 64, 8), (16, 1, 128, 32),
                                              (6, 2, 192, 64), (2, 1, 256, 128)])
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("nsplit", [1, 3])
-def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
+@pytest.mark.parametrize("nsplit, cluster", [(1, False), (3, False), (3, True), (5, True), (8, True)])
+def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit, cluster):
+    """Slices of the keys merged through global partials (cluster False) or through the distributed shared
+    memory of a thread-block cluster, which needs no partial buffers."""
     g = nq // nkv
     ql = max(1, min(3, 16 // g))
     lens_q, lens_kv = [1, ql, 1, 1, ql], [1, 40, 65, 300, 129]
@@ -403,12 +405,14 @@ def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
     kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
     n = len(lens_q)
     chunk = ((max(lens_kv) + nsplit - 1) // nsplit + 63) // 64 * 64
-    part_o = torch.full((n * nkv * nsplit * 16, hd), float("nan"), device=DEV)
-    part_ml = torch.full((n * nkv * nsplit * 16, 2), float("nan"), device=DEV)
+    part_o = part_ml = None
+    if not cluster:
+        part_o = torch.full((n * nkv * nsplit * 16, hd), float("nan"), device=DEV)
+        part_ml = torch.full((n * nkv * nsplit * 16, 2), float("nan"), device=DEV)
     out = torch.full_like(q, float("nan"))
     scale = 1 / math.sqrt(hd)
     ops().paged_attention_decode_tma(q, kc, vc, out, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
-                                     part_o, part_ml)
+                                     part_o, part_ml, cluster=cluster)
     assert ops().gemm_error_flag(q.device) == 0
     kc[~used.to(DEV)] = 0
     vc[~used.to(DEV)] = 0
@@ -421,7 +425,7 @@ def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit):
             kc[t[-1], :, kv % ps:] = float("nan")
     out2 = torch.full_like(q, float("nan"))
     ops().paged_attention_decode_tma(q, kc, vc, out2, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk, nsplit,
-                                     part_o, part_ml)
+                                     part_o, part_ml, cluster=cluster)
     assert torch.equal(out, out2)
 
 
