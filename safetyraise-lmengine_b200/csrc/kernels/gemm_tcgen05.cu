@@ -169,7 +169,22 @@ struct GemmArgs {
   int* tile_counters;      // one per output tile, zero on entry (split-K only)
   int swiglu8;             // 1: weight rows come in blocks of 16 (8 gate rows, then the 8 up rows of the same
                            //    features); the output is silu(gate) * up, [M, N/2]
+  int clustered;           // 1: the splits of a tile are one thread-block cluster (along z) and add their sums
+                           //    through distributed shared memory; partial and tile_counters are not used
 };
+
+__device__ __forceinline__ void cluster_sync_all() {   // every thread of every block of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes at `mine` (an address in this block's shared memory) in block `rank` of the cluster
+__device__ __forceinline__ float4 peer_f32x4(const float* mine, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(mine)), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
 
 // x * logistic(x) (src/model/math.rs:11-22) in float32 with the fast exponential and reciprocal:
 // one branch-free form serves both signs here, since exp2 of a large argument is +inf and its
@@ -244,6 +259,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // the epilogue warps' state (warps 2..5); thread (ew, lane) writes the tokens m_first, m_first + m_step, ...
+  constexpr int SROW = BM + 4;                        // floats per token row of the slab (padded)
+  static_assert(BN * SROW * 4 <= STAGES * STAGE, "the epilogue's slab lives in the ring");
+  float* slab = reinterpret_cast<float*>(smem);      // [BN tokens][SROW]
+  const int ew = warp & 3;
+  const int rows = min(BN, args.M - m0);
+  bool finish = false;
+  int m_first = ew, m_step = 4;
+
   if (warp == 0) {
     if (lane == 0) {
       // Weights are written by no kernel, so the first stages' weight tiles are requested before the
@@ -299,14 +323,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     pdl_wait();
     const bool ok = mbar_wait(accum_bar, 0, args.err_flag, 3);
     tcgen05_fence_after();
-    const int ew = warp & 3;
     const int lane_base = 32 * ew;                      // the TMEM lanes this warp may read
     constexpr int CH = BN < 32 ? 16 : 32;
-    constexpr int SROW = BM + 4;                        // floats per token row of the slab (padded)
-    static_assert(BN * SROW * 4 <= STAGES * STAGE, "the epilogue's slab lives in the ring");
-    float* slab = reinterpret_cast<float*>(smem);      // [BN tokens][SROW]
-    const bool split = gridDim.z > 1;
-    const int rows = min(BN, args.M - m0);
+    const bool split = gridDim.z > 1 && !args.clustered;
     if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
@@ -318,7 +337,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    bool finish = ok;
+    finish = ok;
     if (split) {
       // this split's sums go out as [split][tile][token][128 weight rows]; the split that arrives last
       // adds all of them in split order (the same order on every run) and writes the result
@@ -366,6 +385,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // up rows sit in another lane's columns)
       if (finish && args.swiglu8) __syncwarp();
     }
+  }
+  if (args.clustered) {
+    // The splits of this tile are the blocks of one cluster, each with its sums in its slab.  Block z
+    // adds the token rows z, z + nz, ... of all slabs in split order (the same on every run) into its
+    // own slab -- rows that no other block reads -- and writes them out below.  Every thread of every
+    // block passes both cluster barriers: no path above leaves the kernel.
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int nz = (int)gridDim.z, z = (int)blockIdx.z;
+      m_first = z + nz * ew;
+      m_step = 4 * nz;
+      for (int m = m_first; m < rows; m += 2 * m_step) {
+        const int m2 = m + m_step < rows ? m + m_step : m;       // two rows at a time: 2 nz loads in flight
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+        for (int p = 0; p < nz; ++p) {
+          const float4 t = peer_f32x4(slab + m * SROW + 4 * lane, (uint32_t)p);
+          const float4 u = peer_f32x4(slab + m2 * SROW + 4 * lane, (uint32_t)p);
+          x.x += t.x; x.y += t.y; x.z += t.z; x.w += t.w;
+          y.x += u.x; y.y += u.y; y.z += u.z; y.w += u.w;
+        }
+        *reinterpret_cast<float4*>(slab + m * SROW + 4 * lane) = x;
+        if (m2 != m) *reinterpret_cast<float4*>(slab + m2 * SROW + 4 * lane) = y;
+      }
+      __syncwarp();                          // SwiGLU reads the up rows from another lane's columns
+    }
+  }
+  if (warp >= 2) {
     if (finish) {
       // rows of the slab -> C
       const int esize = args.c_is_f32 ? 4 : 2;
@@ -376,7 +422,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if ((lane & 3) < 2) {
           const int col = (n0 >> 1) + (lane >> 2) * 8 + (lane & 1) * 4;       // first of 4 columns of C
           const int width = args.N >> 1;
-          for (int m = ew; m < rows; m += 4) {
+          for (int m = m_first; m < rows; m += m_step) {
             const float4 g = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
             const float4 u = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane + 8);
             const float h[4] = {silu_stable(g.x) * u.x, silu_stable(g.y) * u.y, silu_stable(g.z) * u.z,
@@ -402,7 +448,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       } else {
         const int col = n0 + 4 * lane;
-        for (int m = ew; m < rows; m += 4) {
+        for (int m = m_first; m < rows; m += m_step) {
           const float4 x = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
           const float h[4] = {x.x, x.y, x.z, x.w};
           uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + m) * args.ldc + col) * esize;
@@ -426,6 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   }
+  if (args.clustered) cluster_sync_all();       // nobody leaves while another block still reads its slab
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -684,7 +731,26 @@ static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& 
     configured = true;
   }
   dim3 grid((a.N + BM - 1) / BM, (a.M + BN - 1) / BN, splits);
-  launch_pdl(gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, a);
+  if (!a.clustered) {
+    launch_pdl(gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, a);
+    return launched();
+  }
+  // the splits of a tile as one thread-block cluster along z
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, STAGES>, *mw, *mx, a);
   return launched();
 }
 
@@ -735,8 +801,12 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   // a few hundred tokens with a narrow output: token tiles of 256 would leave SMs without a tile
   if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < 148) bn = 128;
-  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0};
-  if (splits > 1) {
+  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0, 0};
+  // up to 8 splits (the portable cluster size) add their sums inside a thread-block cluster and need no
+  // workspace (SRLM_GEMM_CLUSTER=0: through the workspace, as more than 8 splits do)
+  static const bool cluster_off = getenv("SRLM_GEMM_CLUSTER") && !atoi(getenv("SRLM_GEMM_CLUSTER"));
+  a.clustered = splits > 1 && splits <= 8 && !cluster_off;
+  if (splits > 1 && !a.clustered) {
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
     const long long need = 65536 + (long long)splits * tiles * BM * bn * 4;
     if (!workspace || workspace_bytes < need || tiles * 4 > 65536)

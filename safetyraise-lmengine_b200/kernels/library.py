@@ -177,20 +177,26 @@ class KernelLibrary:
         (192 tiles alone would leave the second wave two thirds empty), each split keeping at
         least 4 k-blocks, the partial sums fitting the workspace."""
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < 148:
+            bn = 128                      # as the kernel's entry point chooses
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
         total_kb = (K + 63) // 64
-        if tiles >= 1024 or M > 256:
+        if tiles >= 1024:
             return 1
         if M > 16:
-            # measured on B200 inside decode steps: up to 64 tokens, splitting until about one block per
-            # SM streams (a few more up to 32 tokens) pays (batch 32: 7.9 -> 5.9 ms a step, batch 64:
-            # 9.8 -> 8.5 ms), each split keeping at least 8 k-blocks; beyond 64 tokens the persistent
-            # kernel without a split is faster
-            if M <= 64:
-                sp = max(1, min((222 if M <= 32 else 148) // max(1, tiles), total_kb // 8))
+            # Measured on B200, 8B layer sizes: splitting until about 200 blocks stream (a few more up to 32
+            # tokens) pays, each split keeping at least 8 k-blocks.  Up to 8 splits add their sums inside a
+            # thread-block cluster; with that, 4 splits also pay from 65 to a few hundred tokens, where
+            # an unsplit product of a narrow output leaves most SMs without a tile (128 tokens: o and down
+            # projections 27.6 -> 21.5 us and 64.5 -> 35.6 us).
+            if M <= 32:
+                sp = min(222 // max(1, tiles), total_kb // 8)
+            elif M <= 64:
+                sp = min(200 // max(1, tiles), total_kb // 8, 8)
             else:
-                sp = 1
-            while sp > 1 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
+                sp = min(200 // max(1, tiles), total_kb // 8, 4)
+            sp = max(1, sp)
+            while sp > 8 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
                 sp -= 1
             return sp
         best, best_eff = 1, 0.0

@@ -272,7 +272,10 @@ def test_argmax_ties_go_to_the_lowest_id():
     (1, 128, 64, 1), (8, 384, 96, 1), (16, 192, 64, 1), (17, 200, 72, 1), (33, 4096, 4096, 4),
     (64, 2560, 4096, 1), (64, 512, 1024, 3), (100, 384, 256, 1), (129, 640, 512, 2), (300, 640, 520, 1),
     (2048, 1024, 512, 1), (5, 6144, 4096, None), (8, 4096, 12288, None), (257, 128, 8, 1),
-    (40, 7168, 5120, None), (200, 5120, 17408, 1), (64, 10240, 5120, None), (520, 1280, 25600, 1)])
+    (40, 7168, 5120, None), (200, 5120, 17408, 1), (64, 10240, 5120, None), (520, 1280, 25600, 1),
+    # splits of 2 to 8 add their sums inside a thread-block cluster, more through the workspace
+    (129, 640, 2048, 4), (260, 1000, 1536, 3), (50, 264, 4096, 8), (20, 136, 8192, 12), (64, 4096, 4096, 6),
+    (128, 4096, 12288, None), (256, 6144, 4096, None), (7, 392, 1024, 5)])
 @pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
 def test_gemm_tn_tcgen05(M, N, K, splits, odt):
     g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
@@ -464,7 +467,8 @@ def test_gemm_skinny_finds_each_k_and_row():
 
 
 @pytest.mark.parametrize("M, I, K, splits", [(1, 8, 64, 1), (8, 12288, 512, 1), (5, 24, 72, 1), (16, 256, 96, 1),
-                                             (33, 128, 256, 2), (100, 4096, 512, 1), (64, 512, 2048, 3), (300, 200, 128, 1)])
+                                             (33, 128, 256, 2), (100, 4096, 512, 1), (64, 512, 2048, 3), (300, 200, 128, 1),
+                                             (100, 512, 2048, 4), (200, 136, 1024, 2), (24, 64, 8192, 10)])
 def test_gemm_with_fused_swiglu(M, I, K, splits):
     """Both tensor-core products with the SwiGLU epilogue against product-then-SwiGLU."""
     g = torch.Generator(device=DEV).manual_seed(M + I)
