@@ -171,6 +171,8 @@ struct GemmArgs {
                            //    features); the output is silu(gate) * up, [M, N/2]
   int clustered;           // 1: the splits of a tile are one thread-block cluster (along z) and add their sums
                            //    through distributed shared memory; partial and tile_counters are not used
+  int sk_tiles, sk_blocks; // persistent kernel: the k-blocks of the first sk_tiles tiles are dealt out evenly to
+                           //    the first sk_blocks blocks (0: every block takes whole tiles only)
 };
 
 __device__ __forceinline__ void cluster_sync_all() {   // every thread of every block of the cluster
@@ -487,7 +489,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // the MMAs of the next one are issued, and the shared-memory ring never drains between tiles.
 // The epilogue transposes each 32-token slab through shared memory and writes whole rows of C
 // (256 contiguous bytes per token and tile) instead of one element per lane.
+//
+// Tiles seldom come in multiples of the SM count: 384 tiles leave 60 of 148 SMs idle in the third
+// round.  So the k-blocks of the tiles that do not fill a round (args.sk_tiles of them, the first;
+// see dealt_tiles) are dealt out evenly: block b takes the units [u_lo, u_hi) of the sequence (tile 0, k-block 0),
+// (tile 0, k-block 1), ...; then every block takes whole tiles.  A block that holds only part of a
+// tile's k-blocks writes its sums to its slot of the workspace (float32) and counts itself in;
+// whoever counts in last adds the parts in the order of the blocks -- the same order on every run --
+// and writes the tile.  Nobody waits for anybody.
 // ---------------------------------------------------------------------------
+struct PieceWalk {         // the pieces (tile, k-blocks [kb_lo, kb_hi)) of one block, in the order it runs them
+  int num_kb, total_tiles, sk_tiles, stride;
+  int u, u_hi, dp_t;
+  __device__ PieceWalk(const GemmArgs& a, int num_kb_, int total_tiles_, int block, int blocks)
+      : num_kb(num_kb_), total_tiles(total_tiles_), sk_tiles(a.sk_tiles), stride(blocks) {
+    u = u_hi = 0;
+    if (block < a.sk_blocks) {
+      const int units = a.sk_tiles * num_kb, base = units / a.sk_blocks, rem = units % a.sk_blocks;
+      u = block * base + min(block, rem);
+      u_hi = u + base + (block < rem ? 1 : 0);
+    }
+    dp_t = a.sk_tiles + block;
+  }
+  __device__ bool next(int& t, int& kb_lo, int& kb_hi) {
+    if (u < u_hi) {
+      t = u / num_kb;
+      kb_lo = u - t * num_kb;
+      const int end = min(u_hi, (t + 1) * num_kb);
+      kb_hi = end - t * num_kb;
+      u = end;
+      return true;
+    }
+    if (dp_t < total_tiles) {
+      t = dp_t;
+      kb_lo = 0;
+      kb_hi = num_kb;
+      dp_t += stride;
+      return true;
+    }
+    return false;
+  }
+};
+// first unit of block b's share of the dealt-out units, and the block that holds unit u
+__device__ __forceinline__ int sk_first_unit(int b, int base, int rem) { return b * base + min(b, rem); }
+__device__ __forceinline__ int sk_block_of(int u, int base, int rem) {
+  return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -504,6 +552,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
   uint64_t* acc_full = empty_bar + STAGES;                   // [2]
   uint64_t* acc_empty = acc_full + 2;                        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -534,9 +583,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       pdl_wait();
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+      int t, kb_lo, kb_hi;
+      while (ok && walk.next(t, kb_lo, kb_hi)) {
         const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES, j = it / STAGES;
           ok = mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 21);
           if (!ok) break;
@@ -553,13 +604,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       const uint32_t idesc = umma_idesc_bf16_f32(BN);
       int it = 0, local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+      int t, kb_lo, kb_hi;
+      for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
         const int b = local & 1;
         ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err_flag, 22);   // epilogue has drained it
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + b * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES, j = it / STAGES;
           ok = mbar_wait(&full_bar[s], j & 1, args.err_flag, 23);
           if (!ok) break;
@@ -568,7 +621,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
           const uint64_t adesc = umma_desc_k_sw128(a_addr), bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            tcgen05_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            tcgen05_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb != kb_lo || k != 0) ? 1u : 0u);
           tcgen05_commit(&empty_bar[s]);
         }
         tcgen05_commit(&acc_full[b]);
@@ -585,24 +638,95 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const bool vec_ok = (args.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
     int local = 0, slab_turn = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+    PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+    int t, kb_lo, kb_hi;
+    const int sk_units = args.sk_tiles * num_kb;
+    const int sk_base = args.sk_blocks ? sk_units / args.sk_blocks : 0;
+    const int sk_rem = args.sk_blocks ? sk_units % args.sk_blocks : 0;
+    const int my_first_unit = sk_first_unit(blockIdx.x, sk_base, sk_rem);
+    constexpr size_t SLOT = (size_t)BN * BM;                // floats of a slot: [BN tokens][128 weight rows]
+    for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
       const int b = local & 1;
       const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
       ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err_flag, 24);
       if (!ok) break;
       tcgen05_fence_after();
       const int c0 = args.swiglu8 ? n0 / 2 : n0;           // first column of C of this tile
+      const bool whole = kb_lo == 0 && kb_hi == num_kb;
+      int part_first = 0, part_last = -1;                  // the blocks that share this tile
+      if (!whole) {
+        // this block's sums of a part of the tile's k-blocks -> its slot (0: the piece its share begins
+        // with, 1: the piece it ends with)
+        float* mine = args.partial + (2 * (size_t)blockIdx.x + (t * num_kb + kb_lo == my_first_unit ? 0 : 1)) * SLOT;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += SLAB) {
+          uint32_t v[SLAB];
+          tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
+          tmem_load_wait();
+          if (c + SLAB >= BN) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+          }
+          if (m0 + c >= args.M) continue;
+#pragma unroll
+          for (int j = 0; j < SLAB; ++j) mine[(size_t)(c + j) * BM + lane_base + lane] = __uint_as_float(v[j]);
+        }
+        part_first = sk_block_of(t * num_kb, sk_base, sk_rem);
+        part_last = sk_block_of((t + 1) * num_kb - 1, sk_base, sk_rem);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid_e == 0) {
+          const int prev = atomicAdd(&args.tile_counters[t], 1);
+          const int last = prev == part_last - part_first;
+          if (last) args.tile_counters[t] = 0;              // clean for the next product
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!*last_flag) continue;                          // somebody else finishes this tile
+        __threadfence();
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += SLAB, slab_turn ^= 1) {
         uint32_t v[SLAB];
-        tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
-        tmem_load_wait();
-        if (c + SLAB >= BN) {                               // everything of this tile has left TMEM
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+        if (whole) {
+          tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
+          tmem_load_wait();
+          if (c + SLAB >= BN) {                             // everything of this tile has left TMEM
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+          }
+          if (m0 + c >= args.M) continue;                   // slab beyond the last token (same for all warps)
+        } else {
+          if (m0 + c >= args.M) continue;
+          // the parts of the blocks part_first .. part_last, added in that order; the next part's
+          // loads are in flight while this one is added
+          float acc[SLAB];
+#pragma unroll
+          for (int j = 0; j < SLAB; ++j) acc[j] = 0.f;
+          auto part_of = [&](int pb) {
+            const int which = sk_first_unit(pb, sk_base, sk_rem) >= t * num_kb ? 0 : 1;
+            return args.partial + (2 * (size_t)pb + which) * SLOT + (size_t)c * BM + lane_base + lane;
+          };
+          float got[SLAB], ahead[SLAB];
+          const float* src = part_of(part_first);
+#pragma unroll
+          for (int j = 0; j < SLAB; ++j) got[j] = __ldcg(src + (size_t)j * BM);
+          for (int pb = part_first; pb <= part_last; ++pb) {
+            if (pb < part_last) {
+              const float* nxt = part_of(pb + 1);
+#pragma unroll
+              for (int j = 0; j < SLAB; ++j) ahead[j] = __ldcg(nxt + (size_t)j * BM);
+            }
+#pragma unroll
+            for (int j = 0; j < SLAB; ++j) acc[j] += got[j];
+#pragma unroll
+            for (int j = 0; j < SLAB; ++j) got[j] = ahead[j];
+          }
+#pragma unroll
+          for (int j = 0; j < SLAB; ++j) v[j] = __float_as_uint(acc[j]);
         }
-        if (m0 + c >= args.M) continue;                     // slab beyond the last token (same for all warps)
         uint8_t* sl = slab + slab_turn * SLAB * SLAB_ROW;
         // D[n, m] -> slab[m][column of C]
         if (args.swiglu8) {
@@ -754,8 +878,23 @@ static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& 
   return launched();
 }
 
+// How many tiles (the first ones) the persistent kernel deals out by k-blocks: the ones left over after
+// the whole rounds, when they would leave 40 % of the SMs or more without a tile.  Measured on B200:
+// dealing out more (a whole round's worth with them, or all tiles when there are fewer than SMs) is
+// slower than whole tiles -- blocks that walk the same weight tile no longer do so in step, and what
+// one of them fetched has left the L2 when the next one asks; and a share under 8 k-blocks is not
+// worth its trip through the workspace.
+static int dealt_tiles(int tiles, int num_kb, int sm_count) {
+  const int left = tiles % sm_count;
+  if (tiles <= sm_count || left == 0 || left * 10 > sm_count * 6) return 0;
+  const long long units = (long long)left * num_kb;
+  if (units / 8 < sm_count || left * 4 > 65536) return 0;
+  return left;
+}
+
 template <int BN, int STAGES>
-static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, cudaStream_t stream) {
+static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, long long ws_bytes,
+                             cudaStream_t stream) {
   constexpr int SMEM = STAGES * stage_bytes<BN>() + 2 * 32 * (BM * 4 + 16) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   static int sm_count = 0;
@@ -769,8 +908,19 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
     configured = true;
   }
   const int tiles = ((a.N + BM - 1) / BM) * ((a.M + BN - 1) / BN);
-  const int grid = tiles < sm_count ? tiles : sm_count;
-  launch_pdl(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, a);
+  const int num_kb = (a.K + BK - 1) / BK;
+  GemmArgs b = a;
+  b.sk_tiles = b.sk_blocks = 0;
+  int grid = tiles < sm_count ? tiles : sm_count;
+  const long long slots_bytes = 2ll * sm_count * BN * BM * 4;
+  if (b.partial && b.tile_counters && ws_bytes >= 65536 + slots_bytes) {
+    const int sk = dealt_tiles(tiles, num_kb, sm_count);
+    if (sk > 0) {
+      b.sk_tiles = sk;
+      b.sk_blocks = sm_count;
+    }
+  }
+  launch_pdl(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, b);
   return launched();
 }
 
@@ -820,7 +970,17 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
   if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel (SRLM_GEMM_PERSISTENT=0: one tile per block)
     static const bool off = getenv("SRLM_GEMM_PERSISTENT") && !atoi(getenv("SRLM_GEMM_PERSISTENT"));
-    if (!off) return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, stream) : launch_persistent<256, 4>(mw, mx, a, stream);
+    // SRLM_GEMM_STREAMK=0: whole tiles only
+    static const bool whole_only = getenv("SRLM_GEMM_STREAMK") && !atoi(getenv("SRLM_GEMM_STREAMK"));
+    if (workspace && !whole_only) {
+      a.tile_counters = reinterpret_cast<int*>(workspace);
+      a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 65536);
+    }
+    if (!off)
+      return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, workspace_bytes, stream)
+                       : launch_persistent<256, 4>(mw, mx, a, workspace_bytes, stream);
+    a.tile_counters = nullptr;
+    a.partial = nullptr;
   }
   switch (bn) {
     // stages chosen so that two or three blocks share an SM: their prologues and epilogues overlap one
@@ -832,6 +992,19 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     case 128: return launch<128, 3>(mw, mx, a, splits, stream);
     default: return launch<256, 4>(mw, mx, a, splits, stream);
   }
+}
+
+// How many of the product's tiles the persistent kernel would deal out by k-blocks on the current
+// device (0: whole tiles only, or another kernel serves these sizes); for tests and notes.
+extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < 148) bn = 128;
+  if (bn < 128) return 0;
+  int dev = 0, sm_count = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (sm_count <= 0) return 0;
+  return dealt_tiles(((N + BM - 1) / BM) * ((M + bn - 1) / bn), (K + BK - 1) / BK, sm_count);
 }
 
 // ---------------------------------------------------------------------------

@@ -227,6 +227,11 @@ class KernelLibrary:
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), C.c_int(splits),
             _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()), "gemm_tn_tcgen05")
 
+    def gemm_dealt_tiles(self, M: int, N: int, K: int) -> int:
+        """How many tiles of this product the persistent tensor-core kernel deals out by k-blocks
+        (0: whole tiles only, or another kernel serves these sizes)."""
+        return int(self.lib.srlm_gemm_tcgen05_dealt_tiles(C.c_int(M), C.c_int(N), C.c_int(K)))
+
     def gemm_tn_skinny(self, a, w, out, swiglu8=False):
         """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weight-streaming kernel of decode steps.
         swiglu8: as in gemm_tn_tcgen05."""

@@ -298,6 +298,37 @@ def test_gemm_tn_tcgen05(M, N, K, splits, odt):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("M, N, K", [(900, 6144, 2048), (1300, 4096, 3000), (2048, 6144, 4096), (1100, 24576, 1792)])
+@pytest.mark.parametrize("odt", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_tiles_dealt_out_by_k_blocks(M, N, K, odt):
+    """Sizes whose tiles do not fill the last round: the persistent kernel deals the k-blocks of the
+    left-over tiles out evenly, parts of a tile meet in the workspace and are added in a fixed order."""
+    assert ops().gemm_dealt_tiles(M, N, K) > 0
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, generator=g).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+    ops().gemm_tn_tcgen05(a, w, out)
+    assert ops().gemm_error_flag(a.device) == 0
+    ref = a.float() @ w.float().T
+    if odt == torch.float32:
+        assert torch.allclose(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(K))
+    else:
+        assert torch.allclose(out.float(), ref, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    for _ in range(3):                 # the same bits on every run, and the counters were left clean
+        out2 = torch.full_like(out, float("nan"))
+        ops().gemm_tn_tcgen05(a, w, out2)
+        assert torch.equal(out, out2)
+    # with the SwiGLU epilogue
+    if N % 16 == 0:
+        out3 = torch.full((M, N // 2), float("nan"), device=DEV, dtype=odt)
+        ws = (w.float() / math.sqrt(K) * 2).to(torch.bfloat16)
+        ops().gemm_tn_tcgen05(a, ws, out3, swiglu8=True)
+        full = (a.float() @ ws.float().T).view(M, N // 16, 2, 8)
+        ref3 = (torch.nn.functional.silu(full[:, :, 0]) * full[:, :, 1]).reshape(M, N // 2)
+        assert torch.allclose(out3.float(), ref3, rtol=2e-2, atol=2e-2)
+
+
 def test_gemm_tcgen05_finds_each_k_and_row():
     """Identity-like operands: a misplaced row, column or k block shows as a wrong integer."""
     K, N, M = 256, 256, 40
