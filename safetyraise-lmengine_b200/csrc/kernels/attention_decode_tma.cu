@@ -54,6 +54,19 @@ struct Args {
   float* part_ml;
   int* slice_counters;
   int* err_flag;
+  // Fused with the step before it (head_dim 64, 128 or 256, rotation over the whole head): q and the
+  // step's new keys and values are taken from the projection's output qkv [tokens, (nq + 2 nkv) * hd],
+  // normalised per head (if the weights are given) and rotated here; the new keys and values go to the
+  // cache and, in the block whose slice holds their positions, straight into the tile in shared memory.
+  const bf16* qkv;          // null: q is given and the cache already holds this step's keys and values
+  const float* q_norm_w;
+  const float* k_norm_w;
+  float norm_eps;
+  const float* cos_t;       // [tokens, hd / 2]
+  const float* sin_t;
+  bf16* k_cache;
+  bf16* v_cache;
+  int write_kv;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -135,6 +148,39 @@ __device__ __forceinline__ float peer_f32(const float* mine, uint32_t rank) {
   return v;
 }
 
+// One head of one token, HD = 32 * EPL elements, a lane holding EPL consecutive ones: RMSNorm over the
+// head (if w is given), then the rotation of the pairs (i, i + HD/2), whose halves sit in lanes l and
+// l ^ 16 (src/model/math.rs:25-99).  All 32 lanes call it together.
+template <int EPL>
+struct alignas(2 * EPL) HeadVec { bf16 v[EPL]; };
+template <int EPL>
+__device__ __forceinline__ HeadVec<EPL> norm_rotate_head(const HeadVec<EPL>& raw, const float* w, float eps,
+                                                         const float* cos_row, const float* sin_row, int lane) {
+  constexpr int HD = 32 * EPL;
+  float x[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) x[j] = __bfloat162float(raw.v[j]);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) ss += x[j] * x[j];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) x[j] = x[j] * inv * w[lane * EPL + j];
+  }
+  const bool left = lane < 16;
+  const int i0 = (lane & 15) * EPL;
+  HeadVec<EPL> out;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+    const float c = cos_row[i0 + j], sn = sin_row[i0 + j];
+    out.v[j] = __float2bfloat16_rn(left ? x[j] * c - other * sn : x[j] * c + other * sn);
+  }
+  return out;
+}
+
 // Address of the 16-byte chunk `chunk16` (of head_dim/8) of key `key` in a tile made of panels of
 // 64 dims: [panel][64 keys][128 bytes], 128-byte swizzle (chunk ^= key & 7).
 __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int key, int chunk16) {
@@ -186,7 +232,27 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   // Q rows -> shared memory (plain loads: 16 rows at most), by the consumer warps; the producer warp
   // is already fetching the first tiles
-  if (warp < CONSUMERS) {
+  constexpr bool CAN_FUSE = HD == 64 || HD == 128 || HD == 256;
+  constexpr int EPL = CAN_FUSE ? HD / 32 : 2;
+  const int heads_total = a.nq + 2 * a.nkv;
+  if (CAN_FUSE && a.qkv && warp < CONSUMERS) {
+    // q rows out of the projection's output: a warp per row, normalised and rotated on the way
+#pragma unroll
+    for (int row = warp; row < 16; row += CONSUMERS) {
+      HeadVec<EPL> out;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) out.v[j] = __float2bfloat16_rn(0.f);
+      if (row < rows_total) {
+        const int tok = q0 + row / g;
+        const HeadVec<EPL> raw = *reinterpret_cast<const HeadVec<EPL>*>(
+            a.qkv + ((size_t)tok * heads_total + kvh * g + row % g) * HD + lane * EPL);
+        out = norm_rotate_head<EPL>(raw, a.q_norm_w, a.norm_eps, a.cos_t + (size_t)tok * (HD / 2),
+                                    a.sin_t + (size_t)tok * (HD / 2), lane);
+      }
+      *reinterpret_cast<HeadVec<EPL>*>(q_s + row * (HD + 8) + lane * EPL) = out;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+  } else if (warp < CONSUMERS) {
     for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += CONSUMERS * 32) {
       const int row = idx / (HD / 8), c = idx % (HD / 8);
       uint4 v = make_uint4(0, 0, 0, 0);
@@ -264,6 +330,36 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (!ok) break;
       const uint32_t kt = s32(tiles + s * 2 * TILE_BYTES), vt = kt + TILE_BYTES;
       const int jb = jb0 + t * KT;
+      if (CAN_FUSE && a.qkv && a.write_kv && jb + k_warp + KW > start) {
+        // This step's keys and values among this warp's 16 keys of the tile: no kernel has written them
+        // to the cache yet, so what the TMA copy brought for their rows is stale.  The warp puts them into
+        // the tile (it alone reads these rows) and into the cache for the steps to come; every position
+        // belongs to one slice, one tile and one warp, so each row is written once.
+        const int p_hi = min(min(kv_len, slice_hi), jb + k_warp + KW);
+        for (int p = max(start, jb + k_warp); p < p_hi; ++p) {
+          const int tok = q0 + (p - start);
+          const bf16* src = a.qkv + ((size_t)tok * heads_total + a.nq + kvh) * HD + lane * EPL;
+          const HeadVec<EPL> raw_k = *reinterpret_cast<const HeadVec<EPL>*>(src);
+          const HeadVec<EPL> new_v = *reinterpret_cast<const HeadVec<EPL>*>(src + (size_t)a.nkv * HD);
+          const HeadVec<EPL> new_k = norm_rotate_head<EPL>(raw_k, a.k_norm_w, a.norm_eps,
+                                                           a.cos_t + (size_t)tok * (HD / 2),
+                                                           a.sin_t + (size_t)tok * (HD / 2), lane);
+          const size_t at = (((size_t)table[p / a.page_size] * a.nkv + kvh) * a.page_size + p % a.page_size) * HD +
+                            lane * EPL;
+          *reinterpret_cast<HeadVec<EPL>*>(a.k_cache + at) = new_k;
+          *reinterpret_cast<HeadVec<EPL>*>(a.v_cache + at) = new_v;
+          const int chunk16 = lane * EPL / 8, off = (lane * EPL % 8) * 2;
+          const uint32_t ka = tile_addr(kt, p - jb, chunk16) + off, va = tile_addr(vt, p - jb, chunk16) + off;
+          const uint32_t* kw = reinterpret_cast<const uint32_t*>(&new_k);
+          const uint32_t* vw = reinterpret_cast<const uint32_t*>(&new_v);
+#pragma unroll
+          for (int i = 0; i < EPL / 2; ++i) {
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(ka + 4 * i), "r"(kw[i]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(va + 4 * i), "r"(vw[i]) : "memory");
+          }
+        }
+        __syncwarp();
+      }
       // scores of this warp's 16 keys
       float sc[2][4];
       sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
@@ -811,38 +907,86 @@ extern "C" int srlm_attention_decode_tma_takes(int hd, int page_size) {
 }
 
 // Same contract as srlm_paged_attention_keys (attention_mma.cu); num_pages is the pool's page count.
+namespace srlm {
+namespace dec {
+struct FusedInputs {          // see Args: all null / zero when q is given
+  const void* qkv;
+  const float* q_norm_w;
+  const float* k_norm_w;
+  float eps;
+  const float* cos_t;
+  const float* sin_t;
+  int write_kv;
+};
+static int decode_entry(const void* q, const FusedInputs& f, const void* k_cache, const void* v_cache, void* out,
+                        long long num_pages, const int* block_table, int table_stride, const int* cu_q,
+                        const int* kv_lens, int n_entries, int nq, int nkv, int hd, int page_size, float scale,
+                        int window, int kv_chunk, int nsplit, float* part_o, float* part_ml, int* slice_counters,
+                        int cluster, int* err_flag, cudaStream_t stream) {
+  if (n_entries <= 0) return ST_OK;
+  if (!srlm_attention_decode_tma_takes(hd, page_size) || nq <= 0 || nkv <= 0 || nq % nkv)
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
+  if (f.qkv && ((hd != 64 && hd != 128 && hd != 256) || !f.cos_t || !f.sin_t || ((uintptr_t)f.qkv & 15)))
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: the fused form takes head_dim 64, 128 or 256 with a rotation "
+                  "over the whole head (head_dim %d)", hd);
+  // up to 8 slices (the portable cluster size) can merge through distributed shared memory; more, or
+  // cluster == 0, go through part_o / part_ml and the counters
+  const int clustered = cluster && nsplit > 1 && nsplit <= 8;
+  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % KT ||
+      (nsplit > 1 && !clustered && (!part_o || !part_ml || !slice_counters)))
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
+  if (nsplit > 32 || nkv > 65535)
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d nkv=%d (at most 32 slices: the merge gives a lane to each)",
+                  nsplit, nkv);
+  const int box_rows = page_size < KT ? page_size : KT;
+  const long long rows = num_pages * nkv * page_size;
+  const CUtensorMap* mk = cache_map(k_cache, rows, hd, box_rows);
+  const CUtensorMap* mv = cache_map(v_cache, rows, hd, box_rows);
+  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
+  Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, nq, nkv, hd, page_size,
+         scale * 1.4426950408889634f, window, kv_chunk, nsplit, clustered, part_o, part_ml, slice_counters,
+         err_flag, (const bf16*)f.qkv, f.q_norm_w, f.k_norm_w, f.eps, f.cos_t, f.sin_t,
+         (bf16*)const_cast<void*>(k_cache), (bf16*)const_cast<void*>(v_cache), f.write_kv};
+  switch (hd) {
+    case 64: return launch<64>(mk, mv, a, n_entries, stream);
+    case 128: return launch<128>(mk, mv, a, n_entries, stream);
+    case 192: return launch<192>(mk, mv, a, n_entries, stream);
+    default: return launch<256>(mk, mv, a, n_entries, stream);
+  }
+}
+}  // namespace dec
+}  // namespace srlm
+
 extern "C" int srlm_paged_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                                long long num_pages, const int* block_table, int table_stride,
                                                const int* cu_q, const int* kv_lens, int n_entries, int nq, int nkv,
                                                int hd, int page_size, float scale, int window, int kv_chunk,
                                                int nsplit, float* part_o, float* part_ml, int* slice_counters,
                                                int cluster, int* err_flag, cudaStream_t stream) {
-  if (n_entries <= 0) return ST_OK;
-  if (!srlm_attention_decode_tma_takes(hd, page_size) || nq <= 0 || nkv <= 0 || nq % nkv)
-    return refuse(ST_BAD_SIZE, "attention_decode_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
-  // up to 8 slices (the portable cluster size) can merge through distributed shared memory; more, or
-  // cluster == 0, go through part_o / part_ml and the counters
-  const int clustered = cluster && nsplit > 1 && nsplit <= 8;
-  if (nsplit < 1 || kv_chunk <= 0 || kv_chunk % dec::KT ||
-      (nsplit > 1 && !clustered && (!part_o || !part_ml || !slice_counters)))
-    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d kv_chunk=%d", nsplit, kv_chunk);
-  if (nsplit > 32 || nkv > 65535)
-    return refuse(ST_BAD_SIZE, "attention_decode_tma: nsplit=%d nkv=%d (at most 32 slices: the merge gives a lane to each)",
-                  nsplit, nkv);
-  const int box_rows = page_size < dec::KT ? page_size : dec::KT;
-  const long long rows = num_pages * nkv * page_size;
-  const CUtensorMap* mk = dec::cache_map(k_cache, rows, hd, box_rows);
-  const CUtensorMap* mv = dec::cache_map(v_cache, rows, hd, box_rows);
-  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
-  dec::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, nq, nkv, hd, page_size,
-              scale * 1.4426950408889634f, window, kv_chunk, nsplit, clustered, part_o, part_ml, slice_counters,
-              err_flag};
-  switch (hd) {
-    case 64: return dec::launch<64>(mk, mv, a, n_entries, stream);
-    case 128: return dec::launch<128>(mk, mv, a, n_entries, stream);
-    case 192: return dec::launch<192>(mk, mv, a, n_entries, stream);
-    default: return dec::launch<256>(mk, mv, a, n_entries, stream);
-  }
+  const dec::FusedInputs none{nullptr, nullptr, nullptr, 0.f, nullptr, nullptr, 0};
+  return dec::decode_entry(q, none, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens,
+                           n_entries, nq, nkv, hd, page_size, scale, window, kv_chunk, nsplit, part_o, part_ml,
+                           slice_counters, cluster, err_flag, stream);
+}
+
+// The same with the step before it folded in: q and this step's keys and values come from qkv
+// [tokens, (nq + 2 nkv) * hd], the output of the q/k/v projection.  Per-head RMSNorm of q and k with
+// q_norm_w / k_norm_w [hd] (null: none) and eps, rotation of the pairs (i, i + hd/2) by cos_t / sin_t
+// [tokens, hd/2]; with write_kv the new keys and values are written to the cache (without it the cache
+// must already hold them).  head_dim 64, 128 or 256.
+extern "C" int srlm_paged_attention_decode_fused(const void* qkv, const float* q_norm_w, const float* k_norm_w,
+                                                 float eps, const float* cos_t, const float* sin_t, int write_kv,
+                                                 void* k_cache, void* v_cache, void* out, long long num_pages,
+                                                 const int* block_table, int table_stride, const int* cu_q,
+                                                 const int* kv_lens, int n_entries, int nq, int nkv, int hd,
+                                                 int page_size, float scale, int window, int kv_chunk, int nsplit,
+                                                 float* part_o, float* part_ml, int* slice_counters, int cluster,
+                                                 int* err_flag, cudaStream_t stream) {
+  if (!qkv) return refuse(ST_BAD_SIZE, "attention_decode_fused: no qkv");
+  const dec::FusedInputs f{qkv, q_norm_w, k_norm_w, eps, cos_t, sin_t, write_kv ? 1 : 0};
+  return dec::decode_entry(nullptr, f, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens,
+                           n_entries, nq, nkv, hd, page_size, scale, window, kv_chunk, nsplit, part_o, part_ml,
+                           slice_counters, cluster, err_flag, stream);
 }
 
 // Ragged batch with TMA page loads.  work: n_work pairs (entry, tile of 128 rows); an entry with q tokens has

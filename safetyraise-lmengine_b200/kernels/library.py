@@ -52,6 +52,7 @@ class KernelLibrary:
         self.skinny_max_rows = int(os.environ.get("SRLM_SKINNY_ROWS", str(1 << 30)))
         self.force_cp_async_decode = False
         self.cluster_decode_merge = True        # slices of decode attention merged in a thread-block cluster
+        self.fuse_decode_attention = True       # decode: norm, rotation and append inside the attention kernel
         self.force_mma_sync_prefill = False
 
     @property
@@ -367,6 +368,23 @@ class KernelLibrary:
             C.c_int(kv_chunk), C.c_int(nsplit), _ptr(part_o), _ptr(part_ml), _ptr(counters),
             C.c_int(1 if cluster else 0), _ptr(err), _stream()), "paged_attention_decode_tma")
 
+    def paged_attention_decode_fused(self, qkv, q_norm_w, k_norm_w, eps, cos, sin, write_kv, k_cache, v_cache, out,
+                                     block_table, cu_q, kv_lens, n_entries, nq, nkv, hd, page_size, scale, window,
+                                     kv_chunk, nsplit, part_o=None, part_ml=None, cluster=True):
+        """paged_attention_decode_tma with the step before it folded in: q and the step's new keys and
+        values are read from qkv [tokens, (nq + 2 nkv) * hd], normalised per head (weights may be None)
+        and rotated (cos / sin [tokens, hd/2], pairs (i, i + hd/2)) inside the kernel; with write_kv the
+        new keys and values are written to the cache.  head_dim 64, 128 or 256."""
+        counters = self._slice_counter_buffer(qkv.device, n_entries * nkv) if nsplit > 1 else None
+        err = self._gemm_state(qkv.device)[1]
+        self._check(self.lib.srlm_paged_attention_decode_fused(
+            _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), C.c_float(eps), _ptr(cos), _ptr(sin),
+            C.c_int(int(write_kv)), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]),
+            _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), C.c_int(n_entries),
+            C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+            C.c_int(kv_chunk), C.c_int(nsplit), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+            C.c_int(1 if cluster else 0), _ptr(err), _stream()), "paged_attention_decode_fused")
+
     @staticmethod
     def attention_split(n_entries: int, nkv: int, max_kv: int, max_slices: int = 32):
         """(nsplit, kv_chunk) for the keys-split kernels: as many blocks as run at the same time (two per
@@ -377,6 +395,41 @@ class KernelLibrary:
         chunk = -(-tiles // nsplit) * 64
         nsplit = -(-tiles * 64 // chunk)
         return nsplit, chunk
+
+    def _decode_plan(self, ctx, nkv, hd):
+        """(nsplit, kv_chunk, cluster, part_o, part_ml) for the TMA decode kernel on the batch of ctx."""
+        nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
+        # Up to 8 slices merge inside a thread-block cluster, which saves the round trip through global
+        # memory (6 to 8 us measured); more slices pay only when each of the 8 would have many more
+        # tiles to walk (about 1 us a tile).
+        cluster = False
+        if self.cluster_decode_merge and nsplit > 1:
+            n8, chunk8 = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound, max_slices=8)
+            if chunk8 - chunk <= 7 * 64:
+                nsplit, chunk, cluster = n8, chunk8, True
+        part_o = part_ml = None
+        if nsplit > 1 and not cluster:
+            part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32, reserve=0)
+            part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2, torch.float32,
+                                        reserve=0)
+        return nsplit, chunk, cluster, part_o, part_ml
+
+    def attention_from_projection(self, ctx, qkv, k_cache, v_cache, out, block_table, q_norm_w, k_norm_w, eps, cos,
+                                  sin, rotary_half, write_kv, nq, nkv, hd, page_size, scale, window=0) -> bool:
+        """Decode steps: per-head norm, rotation, append to the cache and attention over the cache in one
+        kernel, straight from the q/k/v projection's output.  Returns False (and does nothing) when the
+        batch or the sizes are not the ones that kernel takes; the caller then runs the steps one by one."""
+        g = nq // nkv
+        if (not self.fuse_decode_attention or qkv.dtype != torch.bfloat16 or ctx.max_q_len * g > 16
+                or hd not in (64, 128, 256) or cos is None or 2 * rotary_half != hd
+                or self.force_simt_attention or self.force_cp_async_decode
+                or not self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))):
+            return False
+        nsplit, chunk, cluster, part_o, part_ml = self._decode_plan(ctx, nkv, hd)
+        self.paged_attention_decode_fused(qkv, q_norm_w, k_norm_w, eps, cos, sin, write_kv, k_cache, v_cache, out,
+                                          block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries, nq, nkv, hd,
+                                          page_size, scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
+        return True
 
     def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
                         window=0):
@@ -389,26 +442,13 @@ class KernelLibrary:
             return
         g = nq // nkv
         if ctx.max_q_len * g <= 16:
-            nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
             if self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size)) and not self.force_cp_async_decode:
-                part_o = part_ml = None
-                # Up to 8 slices merge inside a thread-block cluster, which saves the round trip through
-                # global memory (6 to 8 us measured); more slices pay only when each of the 8 would
-                # have many more tiles to walk (about 1 us a tile).
-                cluster = False
-                if self.cluster_decode_merge and nsplit > 1:
-                    n8, chunk8 = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound, max_slices=8)
-                    if chunk8 - chunk <= 7 * 64:
-                        nsplit, chunk, cluster = n8, chunk8, True
-                if nsplit > 1 and not cluster:
-                    part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,
-                                               reserve=0)
-                    part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2,
-                                                torch.float32, reserve=0)
+                nsplit, chunk, cluster, part_o, part_ml = self._decode_plan(ctx, nkv, hd)
                 self.paged_attention_decode_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
                                                 ctx.n_entries, nq, nkv, hd, page_size, scale, window, chunk,
                                                 nsplit, part_o, part_ml, cluster=cluster)
                 return
+            nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
             part_o = part_ml = None
             if nsplit > 1:
                 part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,

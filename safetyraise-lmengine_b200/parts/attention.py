@@ -76,17 +76,21 @@ class PagedAttention(Part):
         s = self.spec
         T = qkv.shape[0]
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
-        q = ctx.workspace.get("attn.q", T, s.heads * s.head_dim, ctx.dtype)
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
             half = self.position.half
         else:
             cos = sin = None
             half = 0
+        attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
+        if ops.attention_from_projection(ctx, qkv, k_pool, v_pool, attended, ctx.block_tables[group], self.q_norm_w,
+                                         self.k_norm_w, self.eps, cos, sin, half, run_step.writes_cache, s.heads,
+                                         s.kv_heads, s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0):
+            return attended
+        q = ctx.workspace.get("attn.q", T, s.heads * s.head_dim, ctx.dtype)
         ops.qk_norm_rope_append(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, self.eps, cos, sin,
                                 ctx.kv_slot[group], s.heads, s.kv_heads, s.head_dim, half,
                                 write_kv=run_step.writes_cache)
-        attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
         ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
                             s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0)
         return attended

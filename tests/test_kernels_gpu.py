@@ -463,6 +463,74 @@ def test_paged_attention_decode_tma(nq, nkv, hd, ps, window, nsplit, cluster):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("nq, nkv, hd, ps", [(32, 8, 128, 16), (8, 2, 64, 16), (4, 4, 64, 8), (16, 1, 128, 32),
+                                             (2, 1, 256, 128), (6, 3, 128, 64)])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("nsplit, cluster", [(1, False), (3, False), (5, True)])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_decode_attention_from_the_projection(nq, nkv, hd, ps, window, nsplit, cluster, with_norm):
+    """Norm, rotation, append and attention in one kernel against the two kernels one after the other:
+    the same cache contents and the same output, bit for bit; pages of nobody and rows nobody wrote
+    hold NaN.  New positions fall on page edges, tile edges (64) and slice edges."""
+    g = nq // nkv
+    ql = max(1, min(3, 16 // g))
+    lens_q, lens_kv = [1, ql, 1, 1, ql, 1], [1, 40, 65, 300, 129, 64]
+    _, kc, vc, tables, bt, eot, pos = make_paged_case(nq, nkv, hd, ps, torch.bfloat16, lens_q, lens_kv, pages=160)
+    n, T = len(lens_q), sum(lens_q)
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV, generator=gen).to(torch.bfloat16)
+    qw = (1 + 0.3 * torch.randn(hd, device=DEV, generator=gen)) if with_norm else None
+    kw = (1 + 0.3 * torch.randn(hd, device=DEV, generator=gen)) if with_norm else None
+    cos = torch.empty(T, hd // 2, device=DEV)
+    sin = torch.empty_like(cos)
+    ops().rope_table(pos, cos, sin, 10000.0, hd)
+    used = torch.zeros(160, dtype=torch.bool)
+    for t in tables:
+        used[t] = True
+    kc[~used.to(DEV)] = float("nan")
+    vc[~used.to(DEV)] = float("nan")
+    slot = []
+    for t, ql_, kv in zip(tables, lens_q, lens_kv):
+        for p_ in range(kv - ql_, kv):                    # the new positions hold NaN until the step writes them
+            kc[t[p_ // ps], :, p_ % ps] = float("nan")
+            vc[t[p_ // ps], :, p_ % ps] = float("nan")
+            slot.append(t[p_ // ps] * ps + p_ % ps)
+        if kv % ps:
+            kc[t[-1], :, kv % ps:] = float("nan")
+            vc[t[-1], :, kv % ps:] = float("nan")
+    slot = torch.tensor(slot, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(np.cumsum(lens_q)), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens_kv, dtype=torch.int32, device=DEV)
+    chunk = ((max(lens_kv) + nsplit - 1) // nsplit + 63) // 64 * 64
+    scale = 1 / math.sqrt(hd)
+    part_o = part_ml = None
+    if not cluster:
+        part_o = torch.full((n * nkv * nsplit * 16, hd), float("nan"), device=DEV)
+        part_ml = torch.full((n * nkv * nsplit * 16, 2), float("nan"), device=DEV)
+    # one after the other
+    kc1, vc1 = kc.clone(), vc.clone()
+    q1 = torch.empty(T, nq * hd, device=DEV, dtype=torch.bfloat16)
+    out1 = torch.full_like(q1, float("nan"))
+    ops().qk_norm_rope_append(qkv, q1, kc1, vc1, qw, kw, 1e-5, cos, sin, slot, nq, nkv, hd, hd // 2)
+    ops().paged_attention_decode_tma(q1, kc1, vc1, out1, bt, cu, kvl, n, nq, nkv, hd, ps, scale, window, chunk,
+                                     nsplit, part_o, part_ml, cluster=cluster)
+    # in one kernel
+    kc2, vc2 = kc.clone(), vc.clone()
+    out2 = torch.full_like(q1, float("nan"))
+    ops().paged_attention_decode_fused(qkv, qw, kw, 1e-5, cos, sin, True, kc2, vc2, out2, bt, cu, kvl, n, nq, nkv,
+                                       hd, ps, scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
+    assert ops().gemm_error_flag(qkv.device) == 0
+    assert not torch.isnan(out1).any()
+    assert torch.equal(kc1.view(torch.int16), kc2.view(torch.int16))
+    assert torch.equal(vc1.view(torch.int16), vc2.view(torch.int16))
+    assert torch.equal(out1, out2)
+    # without writing: the cache already holds the step's keys and values
+    out3 = torch.full_like(q1, float("nan"))
+    ops().paged_attention_decode_fused(qkv, qw, kw, 1e-5, cos, sin, False, kc1, vc1, out3, bt, cu, kvl, n, nq, nkv,
+                                       hd, ps, scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
+    assert torch.equal(out1, out3)
+
+
 @pytest.mark.parametrize("M, N, K", [(1, 16, 8), (1, 4096, 4096), (8, 6144, 4096), (8, 200, 72), (5, 17, 520),
                                      (9, 384, 96), (16, 4096, 12288), (13, 1000, 264), (8, 151936, 512),
                                      (8, 7168, 5120), (3, 5120, 25600)])
