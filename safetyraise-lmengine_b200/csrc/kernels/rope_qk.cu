@@ -83,64 +83,96 @@ __global__ void qk_norm_rope_append_kernel(
   for (int d = 2 * rotary_half + lane; d < hd; d += 32) put(d, get(d));   // unrotated tail
 }
 
-// The same for bfloat16 with head_dim = 32 * EPL and a rotation over the whole head (rotary_half =
-// head_dim / 2): a lane holds EPL consecutive elements in one vector load, the partner of a pair
-// (i, i + head_dim / 2) sits in lane ^ 16, and every row is read and written once in whole sectors.
-template <int EPL>
+// The same for bfloat16 heads of EPL * LPH elements with a rotation over the whole head (rotary_half =
+// head_dim / 2): LPH lanes (16 or 32) share a head, a lane holds EPL consecutive elements in one vector
+// load, the partner of a pair (i, i + head_dim / 2) sits LPH / 2 lanes away, and every row is read and
+// written once in whole sectors.  A warp takes 32 / LPH heads of one token at a time, PASSES times: the
+// loads of all of them are in flight before the first is used, and the token's cosines and sines are
+// fetched once.  Heads of different kinds may share a warp, so nothing here branches around a shuffle.
+template <int N>
+__device__ __forceinline__ void load_floats(const float* __restrict__ p, float (&out)[N]) {      // p: N * 4-byte aligned
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+  } else {
+    const float2 v = __ldg(reinterpret_cast<const float2*>(p));
+    out[0] = v.x; out[1] = v.y;
+  }
+}
+
+template <int EPL, int LPH, int PASSES>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_append_vec_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
                                bf16* __restrict__ v_cache, const float* __restrict__ q_norm_w,
                                const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
                                const float* __restrict__ sin_t, const int* __restrict__ kv_slot, int T, int nq,
                                int nkv, int heads_total, int write_kv, int page_size) {
-  constexpr int HD = 32 * EPL, HALF = HD / 2;
+  constexpr int HD = EPL * LPH, HALF = HD / 2, HPP = 32 / LPH, HPW = HPP * PASSES;
   struct alignas(2 * EPL) Vec { bf16 v[EPL]; };
+  static_assert((EPL == 2 || EPL % 4 == 0) && (LPH == 16 || LPH == 32), "vector loads; whole heads in a warp");
   pdl_wait();
   pdl_trigger();
+  const int groups = (heads_total + HPW - 1) / HPW;          // head groups per token
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (warp >= T * heads_total) return;
-  const int t = warp / heads_total, head = warp % heads_total;
-  const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
-  if (!is_q && !write_kv) return;
-  const int slot = is_q ? 0 : kv_slot[t];
-  if (!is_q && slot < 0) return;
-  const Vec raw = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads_total + head) * HD + lane * EPL);
-  bf16* dst;
-  if (is_q) {
-    dst = q_out + ((size_t)t * nq + head) * HD;
-  } else {
-    const int kvh = is_k ? head - nq : head - nq - nkv;
-    dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * HD;
-  }
-  if (!is_q && !is_k) {   // value: copy
-    *reinterpret_cast<Vec*>(dst + lane * EPL) = raw;
-    return;
-  }
-  const float* w = is_q ? q_norm_w : k_norm_w;
-  float x[EPL];
+  if (warp >= T * groups) return;
+  const int t = warp / groups, head0 = (warp % groups) * HPW;
+  const int sub = lane / LPH, l = lane % LPH;                 // which head of a pass, which lane of that head
+  const int slot = write_kv ? kv_slot[t] : -1;
+  Vec raw[PASSES];
+  bool live[PASSES];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) x[j] = __bfloat162float(raw.v[j]);
-  if (w) {
+  for (int p = 0; p < PASSES; ++p) {
+    const int head = head0 + p * HPP + sub;
+    live[p] = head < heads_total && (head < nq || slot >= 0);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) raw[p].v[j] = __float2bfloat16_rn(0.f);
+    if (live[p]) raw[p] = *reinterpret_cast<const Vec*>(qkv + ((size_t)t * heads_total + head) * HD + l * EPL);
+  }
+  const int i0 = (l % (LPH / 2)) * EPL;
+  float c[EPL], sn[EPL];
+  load_floats<EPL>(cos_t + (size_t)t * HALF + i0, c);
+  load_floats<EPL>(sin_t + (size_t)t * HALF + i0, sn);
+  const bool left = l < LPH / 2;    // the first half of the lanes holds the elements i of the pairs, the second i + HALF
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int head = head0 + p * HPP + sub;
+    const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+    const float* w = is_q ? q_norm_w : is_k ? k_norm_w : nullptr;
+    float x[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) x[j] = __bfloat162float(raw[p].v[j]);
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) ss += x[j] * x[j];
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) x[j] = x[j] * inv * w[lane * EPL + j];
-  }
-  // lanes 0..15 hold the left elements i of the pairs, lanes 16..31 the right elements i + HALF
-  const bool left = lane < 16;
-  const int i0 = (lane & 15) * EPL;
-  Vec out;
+    for (int off = LPH / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (w) {
+      const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+      float wv[EPL];
+      load_floats<EPL>(w + l * EPL, wv);
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
-    const float c = cos_t[(size_t)t * HALF + i0 + j], sn = sin_t[(size_t)t * HALF + i0 + j];
-    out.v[j] = __float2bfloat16_rn(left ? x[j] * c - other * sn : x[j] * c + other * sn);
+      for (int j = 0; j < EPL; ++j) x[j] = x[j] * inv * wv[j];
+    }
+    Vec out;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[j], LPH / 2);
+      out.v[j] = __float2bfloat16_rn(left ? x[j] * c[j] - other * sn[j] : x[j] * c[j] + other * sn[j]);
+    }
+    if (!live[p]) continue;
+    bf16* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nq + head) * HD;
+    } else {
+      const int kvh = is_k ? head - nq : head - nq - nkv;
+      dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * HD;
+    }
+    *reinterpret_cast<Vec*>(dst + l * EPL) = (is_q || is_k) ? out : raw[p];      // values are copied
   }
-  *reinterpret_cast<Vec*>(dst + lane * EPL) = out;
 }
 
 }  // namespace srlm
@@ -174,13 +206,26 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
   const int heads_total = nq + 2 * nkv;
   const long long warps = (long long)T * heads_total;
   if (act_dtype == DT_BF16 && 2 * rotary_half == hd && (hd == 64 || hd == 128 || hd == 256) &&
-      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
-    const long long grid = (warps * 32 + 255) / 256;
-#define SRLM_ROPE_VEC(EPL)                                                                                        \
-    launch_pdl(qk_norm_rope_append_vec_kernel<EPL>, dim3((unsigned)grid), dim3(256), 0, stream, (const bf16*)qkv,  \
-               (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t, kv_slot, T, nq,  \
-               nkv, heads_total, write_kv, page_size)
-    if (hd == 64) SRLM_ROPE_VEC(2); else if (hd == 128) SRLM_ROPE_VEC(4); else SRLM_ROPE_VEC(8);
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t |
+        (uintptr_t)sin_t | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15) == 0) {
+    // A head per warp and pass (the same order of additions as the attention kernel that does this work
+    // itself in decode steps, so both leave the same bits in the cache; 16 lanes of 8 elements measured no
+    // faster); a warp takes 4 heads when that still gives every SM several warps, else one.
+#define SRLM_ROPE_VEC(EPL, LPH)                                                                                     \
+  do {                                                                                                                \
+    const int per_pass = 32 / (LPH);                                                                                  \
+    const long long w4 = (long long)T * ((heads_total + 4 * per_pass - 1) / (4 * per_pass));                          \
+    if (w4 >= 4096)                                                                                                   \
+      launch_pdl(qk_norm_rope_append_vec_kernel<EPL, LPH, 4>, dim3((unsigned)((w4 * 32 + 255) / 256)), dim3(256),    \
+                 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_norm_w, k_norm_w, eps,  \
+                 cos_t, sin_t, kv_slot, T, nq, nkv, heads_total, write_kv, page_size);                                \
+    else                                                                                                              \
+      launch_pdl(qk_norm_rope_append_vec_kernel<EPL, LPH, 1>,                                                         \
+                 dim3((unsigned)(((long long)T * ((heads_total + per_pass - 1) / per_pass) * 32 + 255) / 256)),       \
+                 dim3(256), 0, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_norm_w,      \
+                 k_norm_w, eps, cos_t, sin_t, kv_slot, T, nq, nkv, heads_total, write_kv, page_size);                 \
+  } while (0)
+    if (hd == 64) SRLM_ROPE_VEC(2, 32); else if (hd == 128) SRLM_ROPE_VEC(4, 32); else SRLM_ROPE_VEC(8, 32);
 #undef SRLM_ROPE_VEC
     return launched();
   }
