@@ -536,13 +536,51 @@ __device__ __forceinline__ int sk_block_of(int u, int base, int rem) {
   return u < rem * (base + 1) ? u / (base + 1) : rem + (u - rem * (base + 1)) / base;
 }
 
-template <int BN, int STAGES>
+// ---- two blocks on one tile (cta_group::2): the even block of the pair issues the MMAs ----------------
+// The address of the same shared-memory object in the even block of the pair.
+__device__ __forceinline__ uint32_t in_even_block(const void* p) { return smem_u32(p) & 0xFEFFFFFFu; }
+// A tiled copy into this block's shared memory that counts its bytes on the even block's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(in_even_block(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this address in both blocks of the pair when the MMAs issued so far are done.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+// An epilogue warp has read its share of an accumulator: tells the block that issues the MMAs.
+template <bool PAIR>
+__device__ __forceinline__ void acc_drained(uint64_t* bar) {
+  if (PAIR) asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(in_even_block(bar)) : "memory");
+  else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
+  // PAIR: two blocks (a cluster of 2, on two SMs) share a tile of 256 weight rows x BN tokens: each
+  // holds its 128 weight rows and half of the tokens in shared memory, the MMAs (cta_group::2, issued by
+  // the even block) read both halves and leave each block's 128 rows of the result in its own TMEM.
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;                 // token rows this block fetches per k-block
+  constexpr int TILE_N = PAIR ? 2 * BM : BM;                 // weight rows of a tile
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2, STAGE = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = 2 * BN;
   constexpr int SLAB = 32;                                   // tokens per epilogue slab
   constexpr int SLAB_ROW = BM * 4 + 16;                      // bytes per token row of the slab (padded)
@@ -556,25 +594,36 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (args.M + BN - 1) / BN, tiles_n = (args.N + BM - 1) / BM;
+  uint32_t rank = 0;                                         // of this block in its pair
+  if (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int walker = PAIR ? blockIdx.x / 2 : blockIdx.x, walkers = PAIR ? gridDim.x / 2 : gridDim.x;
+  const int tiles_m = (args.M + BN - 1) / BN, tiles_n = (args.N + TILE_N - 1) / TILE_N;
   const int total_tiles = tiles_m * tiles_n;
   const int num_kb = (args.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 8 : 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {      // the same warp of both blocks, the same address in both
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();        // both blocks' barriers exist before either signals the other's
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -583,28 +632,37 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       pdl_wait();
       int it = 0;
       bool ok = true;
-      PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+      PieceWalk walk(args, num_kb, total_tiles, walker, walkers);
       int t, kb_lo, kb_hi;
       while (ok && walk.next(t, kb_lo, kb_hi)) {
-        const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
+        const int m0 = (t % tiles_m) * BN + (int)rank * (PAIR ? B_ROWS : 0);
+        const int n0 = (t / tiles_m) * TILE_N + (int)rank * BM;
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES, j = it / STAGES;
           ok = mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 21);
           if (!ok) break;
-          mbar_expect_tx(&full_bar[s], STAGE);
           uint8_t* a = smem + s * STAGE;
-          tma_load_2d(a, &map_w, &full_bar[s], kb * BK, n0);
-          tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], kb * BK, m0);
+          if (PAIR) {
+            // both blocks' copies count on the even block's barrier, which expects the bytes of both
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE);
+            tma_load_2d_pair(a, &map_w, &full_bar[s], kb * BK, n0);
+            tma_load_2d_pair(a + A_BYTES, &map_x, &full_bar[s], kb * BK, m0);
+          } else {
+            mbar_expect_tx(&full_bar[s], STAGE);
+            tma_load_2d(a, &map_w, &full_bar[s], kb * BK, n0);
+            tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], kb * BK, m0);
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16_f32(BN);
+    if (lane == 0 && rank == 0) {
+      // PAIR: M = 256 (field at bit 24, in units of 16 rows)
+      const uint32_t idesc = PAIR ? ((umma_idesc_bf16_f32(BN) & ~(0x1Fu << 24)) | (16u << 24)) : umma_idesc_bf16_f32(BN);
       int it = 0, local = 0;
       bool ok = true;
-      PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+      PieceWalk walk(args, num_kb, total_tiles, walker, walkers);
       int t, kb_lo, kb_hi;
       for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
         const int b = local & 1;
@@ -621,10 +679,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
           const uint64_t adesc = umma_desc_k_sw128(a_addr), bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            tcgen05_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb != kb_lo || k != 0) ? 1u : 0u);
-          tcgen05_commit(&empty_bar[s]);
+            if (PAIR) tcgen05_mma_bf16_pair(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb != kb_lo || k != 0) ? 1u : 0u);
+            else tcgen05_mma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb != kb_lo || k != 0) ? 1u : 0u);
+          if (PAIR) tcgen05_commit_pair(&empty_bar[s]); else tcgen05_commit(&empty_bar[s]);
         }
-        tcgen05_commit(&acc_full[b]);
+        if (PAIR) tcgen05_commit_pair(&acc_full[b]); else tcgen05_commit(&acc_full[b]);
       }
     }
     __syncwarp();
@@ -638,16 +697,16 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const bool vec_ok = (args.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
     int local = 0, slab_turn = 0;
     bool ok = true;
-    PieceWalk walk(args, num_kb, total_tiles, blockIdx.x, gridDim.x);
+    PieceWalk walk(args, num_kb, total_tiles, walker, walkers);
     int t, kb_lo, kb_hi;
     const int sk_units = args.sk_tiles * num_kb;
     const int sk_base = args.sk_blocks ? sk_units / args.sk_blocks : 0;
     const int sk_rem = args.sk_blocks ? sk_units % args.sk_blocks : 0;
-    const int my_first_unit = sk_first_unit(blockIdx.x, sk_base, sk_rem);
+    const int my_first_unit = sk_first_unit(blockIdx.x, sk_base, sk_rem);    // (no shares under PAIR: whole tiles)
     constexpr size_t SLOT = (size_t)BN * BM;                // floats of a slot: [BN tokens][128 weight rows]
     for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
       const int b = local & 1;
-      const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
+      const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * TILE_N + (int)rank * BM;
       ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err_flag, 24);
       if (!ok) break;
       tcgen05_fence_after();
@@ -666,7 +725,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
           if (c + SLAB >= BN) {
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+            if (lane == 0) acc_drained<PAIR>(&acc_empty[b]);
           }
           if (m0 + c >= args.M) continue;
 #pragma unroll
@@ -695,7 +754,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
           if (c + SLAB >= BN) {                             // everything of this tile has left TMEM
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+            if (lane == 0) acc_drained<PAIR>(&acc_empty[b]);
           }
           if (m0 + c >= args.M) continue;                   // slab beyond the last token (same for all warps)
         } else {
@@ -779,9 +838,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();        // neither block leaves while the other may still signal its barriers
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                   : "memory");
   }
 }
 
@@ -884,11 +948,11 @@ static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& 
 // slower than whole tiles -- blocks that walk the same weight tile no longer do so in step, and what
 // one of them fetched has left the L2 when the next one asks; and a share under 8 k-blocks is not
 // worth its trip through the workspace.
-static int dealt_tiles(int tiles, int num_kb, int sm_count) {
-  const int left = tiles % sm_count;
-  if (tiles <= sm_count || left == 0 || left * 10 > sm_count * 6) return 0;
+static int dealt_tiles(int tiles, int num_kb, int walkers) {      // walkers: blocks, or pairs of blocks
+  const int left = tiles % walkers;
+  if (tiles <= walkers || left == 0 || left * 10 > walkers * 6) return 0;
   const long long units = (long long)left * num_kb;
-  if (units / 8 < sm_count || left * 4 > 65536) return 0;
+  if (units / 8 < walkers || left * 8 > 65536) return 0;
   return left;
 }
 
@@ -899,7 +963,7 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
   static bool configured = false;
   static int sm_count = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return refuse((int)e, "gemm_tcgen05: cannot get %d bytes of shared memory", SMEM);
     int dev = 0;
@@ -920,7 +984,49 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
       b.sk_blocks = sm_count;
     }
   }
-  launch_pdl(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, b);
+  launch_pdl(gemm_tcgen05_persistent_kernel<BN, STAGES, false>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, *mw, *mx, b);
+  return launched();
+}
+
+// The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x 256 tokens, a cluster of
+// two blocks per tile, whole tiles only.  mx: the token map with boxes of 128 rows.
+template <int STAGES>
+static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, cudaStream_t stream) {
+  constexpr int BN = 256;
+  constexpr int SMEM = STAGES * (BM * BK * 2 + (BN / 2) * BK * 2) + 2 * 32 * (BM * 4 + 16) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static_assert(SMEM <= 232448, "shared memory of a block");
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return refuse((int)e, "gemm_tcgen05: cannot get %d bytes of shared memory", SMEM);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int tiles = ((a.N + 2 * BM - 1) / (2 * BM)) * ((a.M + BN - 1) / BN);
+  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  GemmArgs b = a;
+  b.sk_tiles = b.sk_blocks = 0;
+  // whole tiles only: dealing the left-over tiles' k-blocks out to the pairs measured slower more often
+  // than faster (1,024 tokens: QKV 68.5 against 56.1 us; 4,096 tokens: down 265 against 277 us)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel<BN, STAGES, true>, *mw, *mx, b);
   return launched();
 }
 
@@ -976,6 +1082,13 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
       a.tile_counters = reinterpret_cast<int*>(workspace);
       a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 65536);
     }
+    // token tiles of 256: two SMs per tile of 256 x 256 (SRLM_GEMM_PAIR=0: one SM per tile of 128 x 256)
+    static const bool pair_off = getenv("SRLM_GEMM_PAIR") && !atoi(getenv("SRLM_GEMM_PAIR"));
+    if (!off && bn == 256 && !pair_off) {
+      const CUtensorMap* mx128 = cached_map(X, M, K, ldx, 128, false);
+      if (!mx128) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
+      return launch_pair<6>(mw, mx128, a, stream);
+    }
     if (!off)
       return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, workspace_bytes, stream)
                        : launch_persistent<256, 4>(mw, mx, a, workspace_bytes, stream);
@@ -1004,6 +1117,8 @@ extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (sm_count <= 0) return 0;
+  static const bool pair_off = getenv("SRLM_GEMM_PAIR") && !atoi(getenv("SRLM_GEMM_PAIR"));
+  if (bn == 256 && !pair_off) return 0;       // pairs of SMs on tiles of 256 x 256: whole tiles
   return dealt_tiles(((N + BM - 1) / BM) * ((M + bn - 1) / bn), (K + BK - 1) / BK, sm_count);
 }
 
