@@ -34,6 +34,7 @@ constexpr int BM = 128;            // weight rows per tile (MMA M)
 constexpr int BK = 64;             // bf16 elements per k block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int BN256_MIN_TILES = 96;   // tiles of 128 weight rows x 256 tokens from which token tiles are 256 wide
 constexpr long long WAIT_CYCLES = 4000000000ll;   // ~2 s: far beyond any real wait
 
 // ---------------------------------------------------------------------------
@@ -988,11 +989,10 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
   return launched();
 }
 
-// The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x 256 tokens, a cluster of
-// two blocks per tile, whole tiles only.  mx: the token map with boxes of 128 rows.
-template <int STAGES>
+// The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x BN tokens, a cluster of
+// two blocks per tile, whole tiles only.  mx: the token map with boxes of BN / 2 rows.
+template <int BN, int STAGES>
 static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, cudaStream_t stream) {
-  constexpr int BN = 256;
   constexpr int SMEM = STAGES * (BM * BK * 2 + (BN / 2) * BK * 2) + 2 * 32 * (BM * 4 + 16) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static_assert(SMEM <= 232448, "shared memory of a block");
   static bool configured = false;
@@ -1055,8 +1055,10 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   int kb_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  // a few hundred tokens with a narrow output: token tiles of 256 would leave SMs without a tile
-  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < 148) bn = 128;
+  // a few hundred tokens with a narrow output: token tiles of 256 would leave too many SMs without a tile
+  // (measured: worth it from two thirds of the SMs on -- a pair of SMs on 256 x 256 moves half the bytes
+  // per product of two SMs on 128 x 128 each)
+  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0, 0};
   // up to 8 splits (the portable cluster size) add their sums inside a thread-block cluster and need no
   // workspace (SRLM_GEMM_CLUSTER=0: through the workspace, as more than 8 splits do)
@@ -1087,8 +1089,9 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     if (!off && bn == 256 && !pair_off) {
       const CUtensorMap* mx128 = cached_map(X, M, K, ldx, 128, false);
       if (!mx128) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
-      return launch_pair<6>(mw, mx128, a, stream);
+      return launch_pair<256, 6>(mw, mx128, a, stream);
     }
+
     if (!off)
       return bn == 128 ? launch_persistent<128, 5>(mw, mx, a, workspace_bytes, stream)
                        : launch_persistent<256, 4>(mw, mx, a, workspace_bytes, stream);
@@ -1111,7 +1114,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
 // device (0: whole tiles only, or another kernel serves these sizes); for tests and notes.
 extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < 148) bn = 128;
+  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
   if (bn < 128) return 0;
   int dev = 0, sm_count = 0;
   cudaGetDevice(&dev);

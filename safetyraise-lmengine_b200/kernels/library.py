@@ -178,8 +178,10 @@ class KernelLibrary:
         (192 tiles alone would leave the second wave two thirds empty), each split keeping at
         least 4 k-blocks, the partial sums fitting the workspace."""
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < 148:
+        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < 96:
             bn = 128                      # as the kernel's entry point chooses
+        if bn == 256:
+            return 1                      # pairs of SMs on whole tiles of 256 x 256
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
         total_kb = (K + 63) // 64
         if tiles >= 1024:
