@@ -7,9 +7,18 @@
 // prefill of thousands: a weight row is read once whatever the batch.  The
 // accumulator tile D[n, m] sits in TMEM with one weight row per lane; the
 // epilogue reads it with tcgen05.ld and writes C[m, n], 32 consecutive n per
-// warp store.  With split-K (grid.z > 1) each split writes its float32 partial
-// tile to a slab of its own in a workspace, and the last split to finish a tile
-// adds the slabs in split order, so the sum is the same on every run.
+// warp store.
+//
+// Three forms.  (1) One tile per block, for up to 64 tokens and for a few hundred
+// where there are few tiles: K may be split over grid.z; up to 8 splits are a
+// thread-block cluster and add their sums through distributed shared memory,
+// more write float32 partial tiles to a workspace and the last to finish a tile
+// adds them; always in split order, so the sum is the same on every run.
+// (2) Persistent, one block per SM walking over tiles of 128 weight rows x 128
+// tokens with a double-buffered accumulator; the k-blocks of tiles that do not
+// fill a round may be dealt out evenly.  (3) Persistent pairs: two SMs (a cluster
+// of two blocks) on tiles of 256 weight rows x 256 tokens with cta_group::2 MMAs,
+// for many tokens.
 //
 // Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the
 // MMAs, warps 2-5 run the epilogue.  Every wait on an mbarrier is bounded: when
