@@ -195,8 +195,8 @@ def time_prefill(eng, tokens: int, repeats: int):
     import torch
     from safetyraise_lmengine_b200 import StepEntry
     gen = torch.Generator().manual_seed(1)
-    best = None
-    for i in range(repeats + 1):
+    times = []
+    for i in range(repeats + 3):
         toks = torch.randint(0, eng.spec.vocab_size, (tokens,), generator=gen).tolist()
         s = eng.open_request()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -206,10 +206,10 @@ def time_prefill(eng, tokens: int, repeats: int):
         b.record()
         torch.cuda.synchronize()
         eng.close_request(s)
-        if i > 0:                      # the first run warms up
-            t = a.elapsed_time(b)
-            best = t if best is None else min(best, t)
-    return best
+        if i >= 3:                     # three runs warm up
+            times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]      # the median
 
 
 def time_e2e(eng, batch: int, context: int, steps: int, warmup: int):
@@ -272,7 +272,7 @@ def main() -> int:
     eng = build_engine(args.layers, max_requests=big, tokens_in_cache=big * (CONTEXT + 256) + PREFILL_TOKENS,
                        max_batch_tokens=PREFILL_TOKENS, graphs=not args.no_graphs)
     if args.only_prefill:
-        pf_ms = time_prefill(eng, PREFILL_TOKENS, 2)
+        pf_ms = time_prefill(eng, PREFILL_TOKENS, 5)
         print(json.dumps({"prefill_ms": pf_ms, "tokens": PREFILL_TOKENS}))
         return 0
     slots = fill_contexts(eng, B, CONTEXT)
@@ -311,7 +311,7 @@ def main() -> int:
             for s in sl:
                 eng.close_request(s)
         out["points"] = points
-        pf_ms = time_prefill(eng, PREFILL_TOKENS, 2)
+        pf_ms = time_prefill(eng, PREFILL_TOKENS, 5)
         flops = prefill_flops(eng.spec, PREFILL_TOKENS)
         out["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms / 1000.0), 1), "tokens": PREFILL_TOKENS,
                           "ms": round(pf_ms, 3),
