@@ -1,0 +1,35 @@
+"""The host-side plans of the kernel library (no GPU): how keys are cut into slices and K into splits."""
+import pytest
+
+from safetyraise_lmengine_b200.kernels.library import KernelLibrary
+
+
+@pytest.mark.parametrize("n_entries", [1, 2, 3, 8, 17, 64, 300])
+@pytest.mark.parametrize("nkv", [1, 2, 8])
+@pytest.mark.parametrize("max_kv", [1, 63, 64, 65, 2083, 8192, 40000])
+@pytest.mark.parametrize("cap", [8, 32])
+def test_attention_split_covers_every_key_in_whole_tiles(n_entries, nkv, max_kv, cap):
+    nsplit, chunk = KernelLibrary.attention_split(n_entries, nkv, max_kv, max_slices=cap)
+    assert 1 <= nsplit <= cap
+    assert chunk > 0 and chunk % 64 == 0
+    assert nsplit * chunk >= max_kv                       # every key lies in a slice
+    assert (nsplit - 1) * chunk < max(max_kv, 1) + 63     # and no slice is empty
+    # within one wave of two blocks per SM, unless a single slice per pair is already more
+    assert nsplit == 1 or n_entries * nkv * nsplit <= 296
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16, 17, 32, 33, 64, 65, 128, 129, 300, 512, 1024, 2048, 5000])
+@pytest.mark.parametrize("N, K", [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096),
+                                  (200, 72), (128, 64), (1024, 25600)])
+def test_gemm_splits_keeps_its_bounds(M, N, K):
+    sp = KernelLibrary.gemm_splits(M, N, K)
+    total_kb = (K + 63) // 64
+    assert 1 <= sp <= max(1, total_kb)
+    if sp > 1:
+        assert total_kb // sp >= 4                        # a split keeps at least a few k-blocks
+    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+    if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) >= 96:
+        assert sp == 1                                    # pairs of SMs on whole tiles of 256 x 256
+    if sp > 8:                                            # beyond a cluster: the partial sums fit the workspace
+        tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
+        assert 65536 + sp * tiles * 128 * bn * 4 <= KernelLibrary.GEMM_WS_BYTES
