@@ -706,3 +706,39 @@ def test_gemm_skinny_with_fused_norms(M, N, K):
     res2 = residual.clone()
     ops().gemm_tn_skinny_fused(x, w1, residual=res2)
     assert torch.equal(res2, res)
+
+
+_FALLBACK_FORMS = r"""
+import math, sys, torch
+from safetyraise_lmengine_b200.kernels import ops
+dev = "cuda:0"
+for M, N, K, splits in [(2048, 6144, 1024, 1), (900, 6144, 2048, 1), (512, 6000, 2048, 1), (64, 4096, 4096, 4),
+                        (33, 512, 2048, 3), (128, 4096, 12288, 4), (20, 136, 8192, 12)]:
+    g = torch.Generator(device=dev).manual_seed(M + N)
+    a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=dev, generator=g).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=dev)
+    ops.gemm_tn_tcgen05(a, w, out, splits=splits)
+    out2 = torch.full((M, N), float("nan"), device=dev)
+    ops.gemm_tn_tcgen05(a, w, out2, splits=splits)
+    ref = a.float() @ w.float().T
+    assert ops.gemm_error_flag(a.device) == 0
+    assert torch.allclose(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(K)), (M, N, K, splits)
+    assert torch.equal(out, out2), (M, N, K, splits)
+print("fallback forms agree")
+"""
+
+
+def test_gemm_tcgen05_forms_behind_the_switches():
+    """The forms that the defaults no longer reach: one SM per tile of 128 x 256 (no pairs), whole tiles only
+    (no dealing), K splits through the workspace (no cluster).  The switches are read once per process,
+    hence a process of its own."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SRLM_GEMM_PAIR="0", SRLM_GEMM_STREAMK="0", SRLM_GEMM_CLUSTER="0",
+               PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    done = subprocess.run([sys.executable, "-c", _FALLBACK_FORMS], env=env, capture_output=True, text=True,
+                          timeout=300)
+    assert done.returncode == 0 and "fallback forms agree" in done.stdout, done.stdout[-2000:] + done.stderr[-2000:]
