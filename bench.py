@@ -6,10 +6,13 @@ A "step" is one decode step: every request of the batch gets its next token.
 The default run has the sizes of the 8B configuration (36 layers, hidden 4096,
 32/8 heads of 128, intermediate 12288, vocabulary 151936), random weights in
 bfloat16, a batch of 8 and 2,048 tokens of context per request.  It prints one
-JSON line: decoded tokens a second on the device (`value`), the same through
-the Python entry point with host tokens in and out (`e2e`), a 2,048-token
-prefill, the decode step's fraction of the HBM roofline, and decode at batch 1
-and 64.
+JSON line: decoded tokens a second on the device (`value`: CUDA events around
+the device half of each step -- the upload of the batch and the forward; the
+host half, checks and batch layout, is done before the first event), the same
+through the Python entry point by the wall clock with host tokens in and out
+(`e2e`), a 2,048-token prefill (the median of runs back to back: the GPU is at
+its power cap by then), the decode step's fraction of the HBM roofline, and
+decode at batch 1 and 64.
 """
 from __future__ import annotations
 
