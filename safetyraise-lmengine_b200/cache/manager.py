@@ -174,6 +174,15 @@ class CacheManager:
             raise ValueError(f"slot {slot} is not open")
         return list(self._table_buf[:n])
 
+    def table_into(self, group: str, slot: int, out) -> int:
+        """Writes the slot's block table into ``out`` (a contiguous int32 numpy array) and returns its
+        length (entries beyond len(out) are not written)."""
+        n = self._lib.srlm_cache_table(self._h, self._paged_index[group], slot,
+                                       out.ctypes.data_as(C.POINTER(C.c_int32)), len(out))
+        if n < 0:
+            raise ValueError(f"slot {slot} is not open")
+        return n
+
     def free_pages(self, group: Optional[str] = None) -> int:
         return self._lib.srlm_cache_free_pages(self._h, self._paged_index[group] if group else 0)
 

@@ -148,10 +148,15 @@ class Engine:
                 raise ShapeError(f"slot {e.slot} is not open")
             if start + n > self.max_context:
                 raise ShapeError(f"slot {e.slot}: {start}+{n} tokens exceed the context of {self.max_context}")
-            ids = np.asarray(e.tokens, dtype=np.int64)
-            wrong = ((ids < 0) | (ids >= vocab)) & (ids != LATER)
-            if wrong.any():
-                raise ShapeError(f"token id {int(ids[wrong][0])} is outside the vocabulary of {vocab}")
+            if n == 1:                               # a decoded token: no array for one number
+                t = int(e.tokens[0])
+                if not (0 <= t < vocab or t == LATER):
+                    raise ShapeError(f"token id {t} is outside the vocabulary of {vocab}")
+            else:
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                wrong = ((ids < 0) | (ids >= vocab)) & (ids != LATER)
+                if wrong.any():
+                    raise ShapeError(f"token id {int(ids[wrong][0])} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ShapeError(f"wanted place {w} is outside the entry's {n} tokens")
@@ -211,25 +216,37 @@ class Engine:
         cu[0] = 0
         t0 = r0 = 0
         token_at, missing = [], 0
-        tables = {g.name: [self.cache.table(g.name, e.slot) for e in entries] for g in groups}
+        slot_views = [(view("kv_slot:" + g.name), view("table:" + g.name), g.name) for g in groups]
         for i, e in enumerate(entries):
             q = q_lens[i]
-            ids = np.asarray(e.tokens, dtype=np.int32)
-            missing += int((ids == LATER).sum())
             token_at.append(sections["token_ids"][0] + t0)
-            tok[t0:t0 + q] = ids
-            posv[t0:t0 + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
-            eot[t0:t0 + q] = i
+            if q == 1:                               # a decoded token: plain numbers
+                t = int(e.tokens[0])
+                missing += t == LATER
+                tok[t0] = t
+                posv[t0] = starts[i]
+                eot[t0] = i
+            else:
+                ids = np.asarray(e.tokens, dtype=np.int32)
+                missing += int((ids == LATER).sum())
+                tok[t0:t0 + q] = ids
+                posv[t0:t0 + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
+                eot[t0:t0 + q] = i
             for w in e.want:
                 rows[r0] = t0 + int(w)
                 r0 += 1
-            for g in groups:
-                tab = np.asarray(tables[g.name][i], dtype=np.int32)
-                p = posv[t0:t0 + q]
-                view("kv_slot:" + g.name)[t0:t0 + q] = tab[p // ps] * ps + p % ps
-                tv = view("table:" + g.name)[i * pages:(i + 1) * pages]
-                tv[:len(tab)] = tab
-                tv[len(tab):] = 0
+            for kvs, tabs, name in slot_views:
+                tv = tabs[i * pages:(i + 1) * pages]
+                held = self.cache.table_into(name, e.slot, tv)      # the block table, straight into its row
+                if held > pages:
+                    raise ShapeError(f"slot {e.slot} holds {held} pages, the step laid out {pages}")
+                tv[held:] = 0
+                if q == 1:
+                    p = starts[i]
+                    kvs[t0] = int(tv[p // ps]) * ps + p % ps
+                else:
+                    p = posv[t0:t0 + q]
+                    kvs[t0:t0 + q] = tv[p // ps] * ps + p % ps
             t0 += q
             cu[i + 1] = t0
         view("slots")[:] = [e.slot for e in entries]
