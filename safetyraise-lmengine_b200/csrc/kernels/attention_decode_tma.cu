@@ -16,9 +16,16 @@
 // on to the merge without waiting again, so every block of a cluster reaches
 // the cluster's barriers.
 //
+// For head sizes 64, 128 and 256 with a rotation over the whole head the kernel
+// can also take q and the step's new keys and values straight from the q/k/v
+// projection (see Args::qkv): the consumer warps normalise and rotate the q rows
+// on their way into shared memory, and the warp that owns a new key's row puts
+// the normalised, rotated key and the value into the tile (over what the TMA copy
+// brought for a row nobody had written) and into the cache.
+//
 // Taken when head_dim is a multiple of 64 and page_size is 8, 16, 32 or a
 // multiple of 64; other sizes use the cp.async kernel in attention_mma.cu.
-// Formula: src/model/math.rs:102-155.
+// Formulas: src/model/math.rs:102-155 (attention), :25-99 (norm, rotation).
 #include <cuda.h>
 #include <math_constants.h>
 
