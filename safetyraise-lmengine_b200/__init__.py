@@ -17,7 +17,7 @@ def _build_decoder(spec, mctx, source):
     return DecoderModel(spec, mctx, source)
 
 
-register_architecture(_qwen3.ARCHITECTURE, _qwen3.read_spec, _build_decoder)
+register_architecture(_qwen3.ARCHITECTURE, _qwen3.read_spec, _build_decoder, _qwen3.adapt_source)
 
 __version__ = "0.1.0"
 

@@ -40,6 +40,20 @@ class CacheGroupSpec:
             return 0
         return 2 * len(self.entries) * self.kv_heads * self.head_dim * (4 if dtype == torch.float32 else 2)
 
+    def bytes_per_request(self, dtype: torch.dtype, context: int, page_size: int = 1) -> int:
+        """What one request of ``context`` tokens holds in this group at most: its keys and values (of a
+        window group only those the window still covers, in whole pages), or its fixed-size state.
+        Counterpart of state_bytes (src/model/spec.rs:491-522)."""
+        if self.kind == FIXED_STATE:
+            n = 1
+            for d in self.state_shape:
+                n *= d
+            return len(self.entries) * n * self.state_dtype.itemsize
+        tokens = context
+        if self.kind == PAGED_WINDOW and self.window:
+            tokens = min(context, self.window + page_size)
+        return self.bytes_per_token(dtype) * -(-tokens // page_size) * page_size
+
 
 _runtime = None
 
@@ -134,9 +148,7 @@ class CacheManager:
         slot = self._lib.srlm_cache_open(self._h)
         if slot < 0:
             raise ResourceExhausted(f"all {self.max_requests} request slots are taken")
-        for pool in self.state_pools.values():   # a new request starts from a zero state
-            pool[:, slot].zero_()
-        return slot
+        return slot          # the engine zeroes the slot's fixed-size state when it first runs the new occupant
 
     def close_request(self, slot: int) -> None:
         if self._lib.srlm_cache_close(self._h, slot) != 0:

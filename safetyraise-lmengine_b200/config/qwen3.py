@@ -58,6 +58,15 @@ def _eos_ids(text: dict, root: dict, vocab: int):
     return tuple(out)
 
 
+def adapt_source(source):
+    """A checkpoint that holds its text model as ``model.language_model.*`` is read under the plain
+    ``model.*`` names; the output head keeps its name (src/model/native.rs:156-165)."""
+    if "model.language_model.embed_tokens.weight" in set(source.names()):
+        from ..weights.loader import PrefixedSource
+        return PrefixedSource(source, "model.", "model.language_model.")
+    return source
+
+
 def read_spec(root: dict) -> ModelSpec:
     text = root.get("text_config", root)                       # src/model/spec.rs:137
     if text.get("model_type") != MODEL_TYPE:

@@ -10,7 +10,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Callable, Dict
+from typing import Callable, Dict, Optional
 
 from ..errors import ConfigError, Unsupported
 from .spec import ModelSpec
@@ -20,14 +20,19 @@ from .spec import ModelSpec
 class Architecture:
     name: str
     read_spec: Callable[[dict], ModelSpec]
-    build_model: Callable      # (spec, ModelContext) -> model object with the DecoderModel interface
+    build_model: Callable      # (spec, ModelContext, source) -> model object with the DecoderModel interface
+    adapt_source: Optional[Callable] = None   # (weight source) -> weight source under the names the spec uses
+
+    def source_for(self, source):
+        return self.adapt_source(source) if self.adapt_source is not None else source
 
 
 ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, read_spec, build_model) -> Architecture:
-    arch = Architecture(name, read_spec, build_model)
+def register_architecture(name: str, read_spec, build_model, adapt_source=None) -> Architecture:
+    """adapt_source: for checkpoints of the architecture that store the same tensors under other names."""
+    arch = Architecture(name, read_spec, build_model, adapt_source)
     ARCHITECTURES[name] = arch
     return arch
 

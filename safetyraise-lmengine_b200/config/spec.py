@@ -28,9 +28,28 @@ class NormSpec:
 @dataclass(frozen=True)
 class PositionSpec:
     kind: str            # registry key in parts.POSITION_ENCODINGS
-    theta: float
-    rotary_dim: int
-    head_dim: int
+    theta: float = 0.0   # the fields of a rotary encoding; another kind adds its own in a subclass
+    rotary_dim: int = 0
+    head_dim: int = 0
+
+
+@dataclass(frozen=True)
+class AttentionNames:
+    """Tensor names of an attention mixer, each appended to its layer's ``weight_prefix``."""
+    q: str = "self_attn.q_proj.weight"
+    k: str = "self_attn.k_proj.weight"
+    v: str = "self_attn.v_proj.weight"
+    o: str = "self_attn.o_proj.weight"
+    q_norm: str = "self_attn.q_norm.weight"
+    k_norm: str = "self_attn.k_norm.weight"
+
+
+@dataclass(frozen=True)
+class GatedDenseNames:
+    """Tensor names of a gated dense feed-forward, each appended to its layer's ``weight_prefix``."""
+    gate: str = "mlp.gate_proj.weight"
+    up: str = "mlp.up_proj.weight"
+    down: str = "mlp.down_proj.weight"
 
 
 @dataclass(frozen=True)
@@ -50,6 +69,7 @@ class AttentionSpec(MixerSpec):
     softmax_scale: float = 0.0
     window: Optional[int] = None            # None: every earlier key is visible
     bias: bool = False
+    names: AttentionNames = AttentionNames()
 
 
 @dataclass(frozen=True)
@@ -58,6 +78,7 @@ class FeedForwardSpec:
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
+    names: GatedDenseNames = GatedDenseNames()   # read by the gated dense part; other kinds name their own
 
 
 @dataclass(frozen=True)
@@ -68,6 +89,8 @@ class LayerSpec:
     mixer_norm: NormSpec
     feed_forward_norm: NormSpec
     weight_prefix: str                       # e.g. "model.layers.3."
+    mixer_norm_name: str = "input_layernorm.weight"              # appended to weight_prefix
+    feed_forward_norm_name: str = "post_attention_layernorm.weight"
 
 
 @dataclass(frozen=True)
@@ -92,6 +115,8 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm.weight"
     head_name: str = "lm_head.weight"
+    embed_position: Optional[PositionSpec] = None   # an encoding that adds to the embedded tokens (none in Qwen3)
+    embed_position_name: str = "model.embed_positions.weight"
     extra: dict = field(default_factory=dict, compare=False)
 
     def to_json(self) -> dict:

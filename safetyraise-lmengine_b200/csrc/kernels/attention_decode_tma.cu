@@ -833,13 +833,14 @@ static std::map<Key, CUtensorMap> g_maps;
 static std::mutex g_mutex;
 
 // the cache as a matrix [rows = pages * kv_heads * page_size, head_dim]; box = [box_rows, 64 dims]
-static const CUtensorMap* cache_map(const void* ptr, long long rows, int hd, int box_rows) {
+// (copied into *out under the lock: no pointer into the cache of maps leaves this function)
+static bool cache_map(CUtensorMap* out, const void* ptr, long long rows, int hd, int box_rows) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Key key{ptr, rows, hd, box_rows};
   auto it = g_maps.find(key);
-  if (it != g_maps.end()) return &it->second;
+  if (it != g_maps.end()) { *out = it->second; return true; }
   EncodeTiledFn fn = encode_fn();
-  if (!fn) return nullptr;
+  if (!fn) return false;
   CUtensorMap m;
   cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
@@ -848,9 +849,11 @@ static const CUtensorMap* cache_map(const void* ptr, long long rows, int hd, int
   if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return nullptr;
+    return false;
   if (g_maps.size() > 4096) g_maps.clear();
-  return &g_maps.emplace(key, m).first->second;
+  g_maps.emplace(key, m);
+  *out = m;
+  return true;
 }
 
 template <int HD>
@@ -947,9 +950,10 @@ static int decode_entry(const void* q, const FusedInputs& f, const void* k_cache
                   nsplit, nkv);
   const int box_rows = page_size < KT ? page_size : KT;
   const long long rows = num_pages * nkv * page_size;
-  const CUtensorMap* mk = cache_map(k_cache, rows, hd, box_rows);
-  const CUtensorMap* mv = cache_map(v_cache, rows, hd, box_rows);
-  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
+  CUtensorMap mk_copy, mv_copy;
+  const CUtensorMap *mk = &mk_copy, *mv = &mv_copy;
+  if (!cache_map(&mk_copy, k_cache, rows, hd, box_rows) || !cache_map(&mv_copy, v_cache, rows, hd, box_rows))
+    return refuse(ST_BAD_SIZE, "attention_decode_tma: cuTensorMapEncodeTiled refused the cache");
   Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, nq, nkv, hd, page_size,
          scale * 1.4426950408889634f, window, kv_chunk, nsplit, clustered, part_o, part_ml, slice_counters,
          err_flag, (const bf16*)f.qkv, f.q_norm_w, f.k_norm_w, f.eps, f.cos_t, f.sin_t,
@@ -1008,9 +1012,10 @@ extern "C" int srlm_paged_attention_rows_tma(const void* q, const void* k_cache,
     return refuse(ST_BAD_SIZE, "attention_rows_tma: nq=%d nkv=%d hd=%d page_size=%d", nq, nkv, hd, page_size);
   const int box_rows = page_size < dec::KT ? page_size : dec::KT;
   const long long rows = num_pages * nkv * page_size;
-  const CUtensorMap* mk = dec::cache_map(k_cache, rows, hd, box_rows);
-  const CUtensorMap* mv = dec::cache_map(v_cache, rows, hd, box_rows);
-  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_rows_tma: cuTensorMapEncodeTiled refused the cache");
+  CUtensorMap mk_copy, mv_copy;
+  const CUtensorMap *mk = &mk_copy, *mv = &mv_copy;
+  if (!dec::cache_map(&mk_copy, k_cache, rows, hd, box_rows) || !dec::cache_map(&mv_copy, v_cache, rows, hd, box_rows))
+    return refuse(ST_BAD_SIZE, "attention_rows_tma: cuTensorMapEncodeTiled refused the cache");
   dec::RowsArgs a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, hd, page_size,
                   scale * 1.4426950408889634f, window, err_flag};
   return hd == 64 ? dec::launch_rows<64>(mk, mv, a, n_work, stream) : dec::launch_rows<128>(mk, mv, a, n_work, stream);

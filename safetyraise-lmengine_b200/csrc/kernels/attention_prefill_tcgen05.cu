@@ -567,13 +567,14 @@ struct Key {
 static std::map<Key, CUtensorMap> g_maps;
 static std::mutex g_mutex;
 
-static const CUtensorMap* cache_map(const void* ptr, long long rows, int box_rows) {
+// copies the map into *out under the lock: no pointer into the cache leaves this function
+static bool cache_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
   std::lock_guard<std::mutex> lock(g_mutex);
   Key key{ptr, rows, box_rows};
   auto it = g_maps.find(key);
-  if (it != g_maps.end()) return &it->second;
+  if (it != g_maps.end()) { *out = it->second; return true; }
   EncodeTiledFn fn = encode_fn();
-  if (!fn) return nullptr;
+  if (!fn) return false;
   CUtensorMap m;
   cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
@@ -582,9 +583,11 @@ static const CUtensorMap* cache_map(const void* ptr, long long rows, int box_row
   if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return nullptr;
+    return false;
   if (g_maps.size() > 4096) g_maps.clear();
-  return &g_maps.emplace(key, m).first->second;
+  g_maps.emplace(key, m);
+  *out = m;
+  return true;
 }
 
 }  // namespace fmha
@@ -612,9 +615,10 @@ extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k
                   nkv, hd, page_size, tiles_per_block);
   const int box_rows = page_size < fmha::KT ? page_size : fmha::KT;
   const long long rows = num_pages * nkv * page_size;
-  const CUtensorMap* mk = fmha::cache_map(k_cache, rows, box_rows);
-  const CUtensorMap* mv = fmha::cache_map(v_cache, rows, box_rows);
-  if (!mk || !mv) return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: cuTensorMapEncodeTiled refused the cache");
+  CUtensorMap mk_copy, mv_copy;
+  const CUtensorMap *mk = &mk_copy, *mv = &mv_copy;
+  if (!fmha::cache_map(&mk_copy, k_cache, rows, box_rows) || !fmha::cache_map(&mv_copy, v_cache, rows, box_rows))
+    return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: cuTensorMapEncodeTiled refused the cache");
   constexpr int SMEM = 2 * fmha::TILE_BYTES + fmha::KV_STAGES * 2 * fmha::TILE_BYTES + 24 * 8 + 1024;
   static bool configured = false;
   if (!configured) {

@@ -145,6 +145,21 @@ __global__ void residual_add_kernel(float* __restrict__ residual, const TA* __re
     residual[i] += to_float(delta[i]);
 }
 
+// flag[0] = 1 if any a[i] (+ b[i], when b is given) is NaN or infinite.
+template <typename TB>
+__global__ void check_finite_kernel(const float* __restrict__ a, const TB* __restrict__ b, size_t n,
+                                    int* __restrict__ flag) {
+  pdl_wait();
+  pdl_trigger();
+  bool bad = false;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float x = a[i];
+    if (b) x += to_float(b[i]);
+    bad |= !(fabsf(x) <= 3.402823466e+38f);
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch(flag, 1);
+}
+
 static inline int norm_block(int H) {
   int b = 32;
   while (b < 1024 && b * 4 < H) b <<= 1;
@@ -224,5 +239,17 @@ extern "C" int srlm_residual_add(float* residual, const void* delta, int act_dty
   if (n <= 0) return ST_OK;
   SRLM_DISPATCH_ACT(act_dtype, TA, (residual_add_kernel<TA><<<flat_grid((size_t)n, 256), 256, 0, stream>>>(
       residual, (const TA*)delta, (size_t)n)));
+  return launched();
+}
+
+// The non-finite test of a step (src/model/native.rs:276-278, 292-294): a [n] float32, b [n] of the
+// activation dtype or null; flag[0] becomes 1 if any a[i] + b[i] is NaN or infinite.
+extern "C" int srlm_check_finite(const float* a, const void* b, int b_dtype, long long n, int* flag,
+                                 cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (!flag) return refuse(ST_BAD_SIZE, "check_finite: no flag");
+  const int grid = flat_grid((size_t)n, 256);
+  SRLM_DISPATCH_ACT(b_dtype, TB, launch_pdl(check_finite_kernel<TB>, dim3(grid), dim3(256), 0, stream,
+      a, (const TB*)b, (size_t)n, flag));
   return launched();
 }

@@ -903,19 +903,30 @@ struct MapKey {
 };
 static std::map<MapKey, CUtensorMap> g_maps;
 static std::mutex g_maps_mutex;
+static const size_t MAP_CACHE_LIMIT = 4096;
 
-static const CUtensorMap* cached_map(const void* ptr, long long rows, long long K, long long ld, int box_rows,
-                                     bool weight) {
+// Copies the map into *out under the lock: the cache may be emptied by the next lookup (of this thread
+// or another), so no pointer into it ever leaves this function.
+static bool cached_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows,
+                       bool weight) {
   std::lock_guard<std::mutex> lock(g_maps_mutex);
   MapKey key{ptr, rows, K, ld, box_rows};
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     CUtensorMap m;
-    if (!make_map(&m, ptr, rows, K, ld, box_rows, weight)) return nullptr;
-    if (g_maps.size() > 4096) g_maps.clear();
+    if (!make_map(&m, ptr, rows, K, ld, box_rows, weight)) return false;
+    if (g_maps.size() >= MAP_CACHE_LIMIT) g_maps.clear();
     it = g_maps.emplace(key, m).first;
   }
-  return &it->second;
+  *out = it->second;
+  return true;
+}
+
+// For tests: the number of cached maps and the cache's limit.
+extern "C" int srlm_gemm_tcgen05_map_cache(int* limit) {
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  if (limit) *limit = (int)MAP_CACHE_LIMIT;
+  return (int)g_maps.size();
 }
 
 template <int BN, int STAGES>
@@ -1082,9 +1093,10 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     a.tile_counters = reinterpret_cast<int*>(workspace);
     a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 65536);
   }
-  const CUtensorMap* mw = cached_map(W, N, K, ldw, BM, true);
-  const CUtensorMap* mx = cached_map(X, M, K, ldx, bn, false);
-  if (!mw || !mx) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
+  CUtensorMap mw_copy, mx_copy, mx128_copy;
+  const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;
+  if (!cached_map(&mw_copy, W, N, K, ldw, BM, true) || !cached_map(&mx_copy, X, M, K, ldx, bn, false))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
   if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel (SRLM_GEMM_PERSISTENT=0: one tile per block)
     static const bool off = getenv("SRLM_GEMM_PERSISTENT") && !atoi(getenv("SRLM_GEMM_PERSISTENT"));
     // SRLM_GEMM_STREAMK=0: whole tiles only
@@ -1096,8 +1108,8 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     // token tiles of 256: two SMs per tile of 256 x 256 (SRLM_GEMM_PAIR=0: one SM per tile of 128 x 256)
     static const bool pair_off = getenv("SRLM_GEMM_PAIR") && !atoi(getenv("SRLM_GEMM_PAIR"));
     if (!off && bn == 256 && !pair_off) {
-      const CUtensorMap* mx128 = cached_map(X, M, K, ldx, 128, false);
-      if (!mx128) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
+      const CUtensorMap* mx128 = &mx128_copy;
+      if (!cached_map(&mx128_copy, X, M, K, ldx, 128, false)) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
       return launch_pair<256, 6>(mw, mx128, a, stream);
     }
 

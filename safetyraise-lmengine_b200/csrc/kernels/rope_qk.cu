@@ -4,6 +4,7 @@
 // Formulas: per-head norm src/model/native.rs:629-634, rotation
 // src/model/math.rs:52-99 (half-split pairs (i, i+half), angle =
 // pos / theta^(2i/rotary_dim)), append before attending src/model/native.rs:637.
+// The scalar kernel also takes interleaved pairs (2i, 2i+1), which other encodings use.
 // The angle is formed in double precision and rounded once, so cos and sin are
 // exact to float32 at every position.
 #include "common.cuh"
@@ -35,7 +36,7 @@ __global__ void qk_norm_rope_append_kernel(
     TC* __restrict__ v_cache, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
     float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     const int* __restrict__ kv_slot, int T, int nq, int nkv, int hd, int rotary_half,
-    int heads_total, int write_kv, int page_size) {
+    int heads_total, int write_kv, int page_size, int interleaved) {
   pdl_wait();
   pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -75,10 +76,11 @@ __global__ void qk_norm_rope_append_kernel(
   const float* cs = cos_t + (size_t)t * rotary_half;
   const float* sn = sin_t + (size_t)t * rotary_half;
   for (int i = lane; i < rotary_half; i += 32) {
-    const float l = get(i), r = get(i + rotary_half);
+    const int li = interleaved ? 2 * i : i, ri = interleaved ? 2 * i + 1 : i + rotary_half;
+    const float l = get(li), r = get(ri);
     const float c = cs[i], s = sn[i];
-    put(i, l * c - r * s);
-    put(i + rotary_half, r * c + l * s);
+    put(li, l * c - r * s);
+    put(ri, r * c + l * s);
   }
   for (int d = 2 * rotary_half + lane; d < hd; d += 32) put(d, get(d));   // unrotated tail
 }
@@ -195,7 +197,7 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
                                         const float* k_norm_w, float eps, const float* cos_t,
                                         const float* sin_t, const int* kv_slot, int T, int nq,
                                         int nkv, int hd, int rotary_half, int write_kv, int page_size,
-                                        cudaStream_t stream) {
+                                        int interleaved, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (nq <= 0 || nkv <= 0 || hd <= 0 || rotary_half < 0 || 2 * rotary_half > hd || page_size <= 0)
     return refuse(ST_BAD_SIZE, "qk_norm_rope_append: nq=%d nkv=%d hd=%d rotary_half=%d", nq, nkv, hd,
@@ -205,7 +207,9 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
                   cache_dtype, act_dtype);
   const int heads_total = nq + 2 * nkv;
   const long long warps = (long long)T * heads_total;
-  if (act_dtype == DT_BF16 && 2 * rotary_half == hd && (hd == 64 || hd == 128 || hd == 256) &&
+  if (rotary_half > 0 && (!cos_t || !sin_t))
+    return refuse(ST_BAD_SIZE, "qk_norm_rope_append: a rotation of %d pairs needs its tables", rotary_half);
+  if (act_dtype == DT_BF16 && !interleaved && 2 * rotary_half == hd && (hd == 64 || hd == 128 || hd == 256) &&
       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t |
         (uintptr_t)sin_t | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15) == 0) {
     // A head per warp and pass (the same order of additions as the attention kernel that does this work
@@ -233,6 +237,6 @@ extern "C" int srlm_qk_norm_rope_append(const void* qkv, void* q_out, int act_dt
   const long long grid = (warps * 32 + block - 1) / block;
   SRLM_DISPATCH_ACT(act_dtype, TA, launch_pdl(qk_norm_rope_append_kernel<TA, TA>, dim3((unsigned)grid), dim3(block), 0, stream,
       (const TA*)qkv, (TA*)q_out, (TA*)k_cache, (TA*)v_cache, q_norm_w, k_norm_w, eps, cos_t, sin_t,
-      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv, page_size));
+      kv_slot, T, nq, nkv, hd, rotary_half, heads_total, write_kv, page_size, interleaved ? 1 : 0));
   return launched();
 }

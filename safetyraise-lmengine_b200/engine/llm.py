@@ -75,7 +75,8 @@ class LLM:
         self.scheduler = Scheduler(engine.cache, config.max_active, config.queue_capacity,
                                    config.prefill_chunk, config.max_batch_tokens,
                                    min(config.max_context, engine.max_context))
-        self.sampler = Sampler(engine.mctx.device, engine.spec.vocab_size, config.max_active)
+        self.sampler = Sampler(engine.mctx.device, engine.spec.vocab_size,
+                               min(config.max_active, engine.cache.max_requests), status=engine.status)
         self.eos = set(engine.spec.eos_token_ids)
         self._live: Dict[int, RequestState] = {}
         self._done: Dict[int, RequestState] = {}
@@ -237,7 +238,16 @@ class LLM:
             logits, [s.request.sampling for s in states], [s.seed for s in states],
             [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
         ahead = self._plan_ahead(plan, sampled, states)        # overlaps the device's work
-        tokens = self.sampler.collect(rows)                     # waits for the device
+        tokens = self.sampler.collect(rows)                     # waits for the device; the fault words come along
+        fault = self.engine.fault_of(self.sampler.last_words)
+        if fault is not None:
+            # the step's result cannot be trusted: none of its tokens is published, every request of
+            # the step ends with an error and gives its pages and its slot back
+            # (src/engine/scheduler.rs:882-895)
+            self._discard_prepared()
+            prep.state_snapshot = None
+            self._fail_plan(plan, fault)
+            return True
         if not ahead:
             for p in plan:
                 self.scheduler.advance(p.request_id, p.count)

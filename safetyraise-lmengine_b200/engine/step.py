@@ -22,8 +22,8 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..config.registry import architecture_of, read_config_json
-from ..errors import ConfigError, ResourceExhausted, ShapeError, Unavailable
-from ..parts.base import ModelContext, StepContext, Workspace
+from ..errors import ConfigError, ResourceExhausted, ShapeError, StepFailed, Unavailable
+from ..parts.base import FAULT_LOGITS, FAULT_NAMES, STATUS_WORDS, ModelContext, StepContext, Workspace
 from ..weights.safetensors_io import WeightFolder
 
 DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16,
@@ -38,6 +38,8 @@ class StepEntry:
     slot: int
     tokens: Sequence[int]             # LATER for an id that PreparedStep.set_token supplies before run()
     want: Sequence[int] = ()          # indices into ``tokens`` whose logits are returned
+    generation: Optional[int] = None  # the slot's generation when the request opened it (``Engine.generation``);
+                                      # given, a step refuses a slot that another request holds by now
 
 
 @dataclass
@@ -55,6 +57,7 @@ class PreparedStep:
     wanted: int
     token_at: List[int]               # offset of each entry's first token id in the buffer
     missing: int                      # token ids still to be set
+    state_snapshot: Optional[dict] = None   # fixed-size state of the step's slots before the forward
 
     def set_token(self, entry: int, index: int, token: int) -> None:
         h = self.pair[0].numpy()
@@ -89,6 +92,11 @@ class Engine:
         self.graph_replays = 0
         self._graph_generation = 0
         self.last_h2d_bytes = 0          # bytes of batch layout the last step copied to the device
+        # fault words of a step (parts.base.FAULT_*), then room for one sampled token per request: a
+        # sampler bound to this buffer brings both back in one read
+        self.status = torch.zeros(STATUS_WORDS + cache.max_requests, dtype=torch.int32, device=mctx.device)
+        self._slot_generation = [0] * cache.max_requests    # the generation of each slot this engine last saw
+        self.steps_failed = 0
 
     # ---- construction -----------------------------------------------------
     @classmethod
@@ -108,6 +116,7 @@ class Engine:
             raise ConfigError(f"dtype {dtype!r}: float32 or bfloat16")
         arch = architecture_of(config)
         spec = arch.read_spec(config)
+        source = arch.source_for(source)
         device = torch.device(device)
         mctx = ModelContext(device, tdtype, max_batch_tokens, dict(options or {}))
         with torch.cuda.device(device):
@@ -125,6 +134,11 @@ class Engine:
     # ---- requests ---------------------------------------------------------
     def open_request(self) -> int:
         return self.cache.open_request()
+
+    def generation(self, slot: int) -> int:
+        """Grows each time the slot is opened; a StepEntry that carries it is refused once the slot has
+        passed to another request (the owner test of src/model/native.rs:259-261)."""
+        return self.cache.generation(slot)
 
     def close_request(self, slot: int) -> None:
         self.cache.close_request(slot)
@@ -146,6 +160,9 @@ class Engine:
             start = self.cache.length(e.slot)
             if start < 0:
                 raise ShapeError(f"slot {e.slot} is not open")
+            if e.generation is not None and e.generation != self.cache.generation(e.slot):
+                raise ShapeError(f"slot {e.slot} was given to another request since this one opened it "
+                                 f"(generation {self.cache.generation(e.slot)}, the entry holds {e.generation})")
             if start + n > self.max_context:
                 raise ShapeError(f"slot {e.slot}: {start}+{n} tokens exceed the context of {self.max_context}")
             if n == 1:                               # a decoded token: no array for one number
@@ -275,7 +292,7 @@ class Engine:
                   "slots": [e.slot for e in prep.entries]},
             cache=self.cache, workspace=self.workspace, dtype=self.mctx.dtype,
             max_q_len=max(prep.q_lens), max_kv_len=max(prep.kv_lens), kv_bound=pages * self.cache.page_size,
-            options=self.mctx.options)
+            options=self.mctx.options, status=self.status[:STATUS_WORDS])
 
     def build_context(self, entries: Sequence[StepEntry], starts: List[int]) -> StepContext:
         """Flattens the batch, uploads it in one copy and returns the device views."""
@@ -316,6 +333,7 @@ class Engine:
         discard() of a step no other step may be prepared or run."""
         self._validate(entries)
         starts = [self.cache.length(e.slot) for e in entries]
+        self._greet_new_occupants(entries)
         done = []
         for e, s in zip(entries, starts):
             if not self.cache.reserve(e.slot, s + len(e.tokens)):
@@ -331,6 +349,16 @@ class Engine:
             self.discard_reservation(entries, starts)
             raise
 
+    def _greet_new_occupants(self, entries) -> None:
+        """A slot that changed hands since this engine last ran it starts from a zero fixed-size state,
+        whoever opened it (this engine, or the scheduler when it admits or re-admits a request)."""
+        for e in entries:
+            g = self.cache.generation(e.slot)
+            if g != self._slot_generation[e.slot]:
+                self._slot_generation[e.slot] = g
+                for pool in self.cache.state_pools.values():
+                    pool[:, e.slot].zero_()
+
     def discard_reservation(self, entries, starts) -> None:
         for e, s in zip(entries, starts):
             self.cache.truncate(e.slot, s)
@@ -339,22 +367,83 @@ class Engine:
         """Gives back what a prepared step reserved; nothing of it ran."""
         self.discard_reservation(prep.entries, prep.starts)
 
-    def run(self, prep: PreparedStep) -> torch.Tensor:
-        """The device half: one copy of the layout, the forward, the new lengths."""
+    def launch(self, prep: PreparedStep) -> torch.Tensor:
+        """The device half without its book-keeping: one copy of the layout, then the forward.  The
+        lengths do not move; ``commit`` or ``revoke`` must follow."""
         if prep.missing:
             self.discard(prep)
             raise ShapeError(f"{prep.missing} token ids of the prepared step were never set")
         try:
             with torch.cuda.device(self.mctx.device):
-                logits = self._forward(self._upload(prep))
+                from ..kernels import ops
+                ops.bind_error_flag(self.status[:1])
+                ctx = self._upload(prep)
+                if self.cache.state_pools:
+                    # fixed-size state cannot be truncated: keep what the step's slots held
+                    # (src/engine/state.rs:222-224 clones the whole state for the same reason)
+                    idx = ctx.slots.long()
+                    prep.state_snapshot = {name: (idx, pool.index_select(1, idx))
+                                           for name, pool in self.cache.state_pools.items()}
+                return self._forward(ctx)
         except Exception:
             self.discard(prep)
             raise
+
+    def commit(self, prep: PreparedStep) -> None:
         for e, s in zip(prep.entries, prep.starts):
             self.cache.commit(e.slot, s + len(e.tokens))
         self.steps_run += 1
+
+    def revoke(self, prep: PreparedStep) -> None:
+        """Takes a launched step back: the fixed-size state of its slots as it was, lengths and pages as
+        before the step.  (After ``commit`` a window group may already have let go of pages the old
+        length needs; such a request can only be closed, which is what the generation loop does.)"""
+        with torch.cuda.device(self.mctx.device):
+            for name, (idx, saved) in (prep.state_snapshot or {}).items():
+                self.cache.state_pools[name].index_copy_(1, idx, saved)
+        prep.state_snapshot = None
+        for e, s in zip(prep.entries, prep.starts):
+            try:
+                self.cache.truncate(e.slot, s)
+            except ValueError:
+                pass
+
+    def read_faults(self):
+        """The fault words, read from the device (waits for it)."""
+        return self.status[:STATUS_WORDS].tolist()
+
+    def fault_of(self, words) -> Optional[StepFailed]:
+        """None if no word is raised; else the error of the failed step, with the words cleared on
+        the device and every recorded graph kept (they write into the same words)."""
+        if not any(words):
+            return None
+        self.status[:STATUS_WORDS].zero_()
+        self.steps_failed += 1
+        what = [f"{FAULT_NAMES.get(i, 'fault word %d' % i)} ({w})" for i, w in enumerate(words) if w]
+        return StepFailed("the step failed and nothing of it was kept: " + "; ".join(what), words)
+
+    def run(self, prep: PreparedStep) -> torch.Tensor:
+        """The device half for a caller that reads the step's fault words itself, together with what
+        it reads back anyway (the generation loop: ``Sampler.collect``): launches, advances the
+        lengths at once so that the next step can be laid out while this one runs, and returns.
+        A raised word then means ``revoke``."""
+        logits = self.launch(prep)
+        self.commit(prep)
         return logits
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step)."""
-        return self.run(self.prepare(entries))
+        """Runs one batch; returns float32 logits [wanted, vocab] (valid until the next step).
+        The lengths advance only after the step's fault words read clean; otherwise everything is
+        taken back and StepFailed is raised (src/model/native.rs:272-306)."""
+        prep = self.prepare(entries)
+        logits = self.launch(prep)
+        with torch.cuda.device(self.mctx.device):
+            from ..kernels import ops
+            if logits.shape[0]:
+                ops.check_finite(logits, None, self.status[FAULT_LOGITS:FAULT_LOGITS + 1])
+        fault = self.fault_of(self.read_faults())
+        if fault is not None:
+            self.revoke(prep)
+            raise fault
+        self.commit(prep)
+        return logits

@@ -28,3 +28,13 @@ class ResourceExhausted(EngineError):
 
 class Unavailable(EngineError):
     """The engine (or its compiled extension) is not usable."""
+
+
+class StepFailed(EngineError):
+    """A step ran and its result cannot be trusted: an activation or a logit was not finite, a token
+    id fell outside the table, or a kernel gave up on a bounded wait.  Nothing of the step was
+    committed (src/model/native.rs:272-306)."""
+
+    def __init__(self, message: str, words=()):
+        super().__init__(message)
+        self.words = tuple(words)

@@ -111,6 +111,13 @@ class KernelLibrary:
         self._check(self.lib.srlm_cast(_ptr(src), dtype_code(src.dtype), _ptr(dst), dtype_code(dst.dtype),
                                        C.c_longlong(src.numel()), _stream()), "cast")
 
+    def check_finite(self, a, b, flag):
+        """flag[0] = 1 if any element of a (+ b, same shape, when given) is NaN or infinite; a float32."""
+        if a.dtype != torch.float32 or (b is not None and b.numel() != a.numel()):
+            raise ShapeError("check_finite: a must be float32 and b of the same size")
+        self._check(self.lib.srlm_check_finite(_ptr(a), _ptr(b), dtype_code(b.dtype) if b is not None else DT_F32,
+                                               C.c_longlong(a.numel()), _ptr(flag), _stream()), "check_finite")
+
     def residual_add(self, residual, delta):
         self._check(self.lib.srlm_residual_add(_ptr(residual), _ptr(delta), dtype_code(delta.dtype),
                                                C.c_longlong(delta.numel()), _stream()), "residual_add")
@@ -122,14 +129,17 @@ class KernelLibrary:
                                              C.c_double(theta), C.c_int(rotary_dim), _stream()), "rope_table")
 
     def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos, sin, kv_slot,
-                            nq, nkv, hd, rotary_half, write_kv=True):
-        """k_cache / v_cache: [pages, kv_heads, page_size, head_dim]; kv_slot[t] = page * page_size + offset."""
+                            nq, nkv, hd, rotary_half, write_kv=True, interleaved=False):
+        """k_cache / v_cache: [pages, kv_heads, page_size, head_dim]; kv_slot[t] = page * page_size + offset.
+        cos / sin [T, rotary_half] rotate the pairs (i, i + rotary_half), or (2i, 2i + 1) when interleaved,
+        of the first 2 * rotary_half elements of every q and k head; rotary_half 0: no rotation."""
         T = qkv.shape[0]
         self._check(self.lib.srlm_qk_norm_rope_append(
             _ptr(qkv), _ptr(q_out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
             dtype_code(k_cache.dtype), _ptr(q_norm_w), _ptr(k_norm_w), C.c_float(eps), _ptr(cos), _ptr(sin),
             _ptr(kv_slot), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(rotary_half),
-            C.c_int(int(write_kv)), C.c_int(k_cache.shape[2]), _stream()), "qk_norm_rope_append")
+            C.c_int(int(write_kv)), C.c_int(k_cache.shape[2]), C.c_int(int(interleaved)), _stream()),
+            "qk_norm_rope_append")
 
     # ---- attention --------------------------------------------------------
     def paged_attention_simt(self, q, k_cache, v_cache, out, block_table, entry_of_token, positions,
@@ -162,10 +172,19 @@ class KernelLibrary:
             ws = torch.zeros(self.GEMM_WS_BYTES, dtype=torch.uint8, device=device)
             err = torch.zeros(1, dtype=torch.int32, device=device)
             st = self._gemm_ws = (ws, err)
+        bound = getattr(self, "_bound_err", None)
+        if bound is not None and bound.device == device:
+            return st[0], bound
         return st
 
+    def bind_error_flag(self, flag: Optional[torch.Tensor]) -> None:
+        """The int32 word that kernels with bounded waits (TMA / tensor-core pipelines) raise when a wait
+        runs out.  An engine binds a word of its own status buffer before each forward, so that the
+        step's read-back sees it; None goes back to the library's own word."""
+        self._bound_err = flag
+
     def gemm_error_flag(self, device) -> int:
-        """Nonzero if a tensor-core GEMM gave up on a wait since the flag was last read (synchronises)."""
+        """Nonzero if a kernel gave up on a bounded wait since the flag was last read (synchronises)."""
         err = self._gemm_state(device)[1]
         v = int(err.item())
         if v:
@@ -416,19 +435,22 @@ class KernelLibrary:
                                         reserve=0)
         return nsplit, chunk, cluster, part_o, part_ml
 
-    def attention_from_projection(self, ctx, qkv, k_cache, v_cache, out, block_table, q_norm_w, k_norm_w, eps, cos,
-                                  sin, rotary_half, write_kv, nq, nkv, hd, page_size, scale, window=0) -> bool:
+    def attention_from_projection(self, ctx, qkv, k_cache, v_cache, out, block_table, q_norm_w, k_norm_w, eps,
+                                  rotation, write_kv, nq, nkv, hd, page_size, scale, window=0) -> bool:
         """Decode steps: per-head norm, rotation, append to the cache and attention over the cache in one
-        kernel, straight from the q/k/v projection's output.  Returns False (and does nothing) when the
-        batch or the sizes are not the ones that kernel takes; the caller then runs the steps one by one."""
+        kernel, straight from the q/k/v projection's output.  rotation: a parts.base.Rotation or None.
+        Returns False (and does nothing) when the batch, the sizes or the rotation (half-split pairs over
+        the whole head) are not the ones that kernel takes; the caller then runs the steps one by one."""
         g = nq // nkv
         if (not self.fuse_decode_attention or qkv.dtype != torch.bfloat16 or ctx.max_q_len * g > 16
-                or hd not in (64, 128, 256) or cos is None or 2 * rotary_half != hd
+                or hd not in (64, 128, 256) or rotation is None or rotation.interleaved
+                or 2 * rotation.pairs != hd
                 or self.force_simt_attention or self.force_cp_async_decode
                 or not self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))):
             return False
         nsplit, chunk, cluster, part_o, part_ml = self._decode_plan(ctx, nkv, hd)
-        self.paged_attention_decode_fused(qkv, q_norm_w, k_norm_w, eps, cos, sin, write_kv, k_cache, v_cache, out,
+        self.paged_attention_decode_fused(qkv, q_norm_w, k_norm_w, eps, rotation.cos, rotation.sin, write_kv,
+                                          k_cache, v_cache, out,
                                           block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries, nq, nkv, hd,
                                           page_size, scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
         return True
@@ -461,6 +483,17 @@ class KernelLibrary:
                                       nq, nkv, hd, page_size, scale, window, chunk, nsplit, part_o, part_ml)
             return
         def work_list(rows_per_block):
+            if ctx.max_q_len == 1:
+                # decode steps (more than 16 query heads per KV head): the list depends on the number of
+                # entries alone, so it is made once and kept on the device; such steps are recorded into
+                # CUDA graphs, and a recording must not hold a copy from a buffer that lives for one step
+                lists = self.__dict__.setdefault("_decode_work_lists", {})
+                key = (q.device, ctx.n_entries, g, rows_per_block)
+                if key not in lists:
+                    tiles = (g + rows_per_block - 1) // rows_per_block
+                    lists[key] = torch.tensor([(e, t) for e in range(ctx.n_entries) for t in range(tiles)],
+                                              dtype=torch.int32).to(q.device)
+                return lists[key]
             work = ctx.tables.get(("attention_rows_work", g, rows_per_block))
             if work is None:
                 # the last row blocks of an entry see the most keys: they go first, so that the long

@@ -16,7 +16,7 @@ from ..config.spec import AttentionSpec, RunStep
 from ..errors import Unsupported
 from ..kernels import ops
 from ..weights.loader import MATRIX, VECTOR, TensorDecl
-from .base import POSITION_ENCODINGS, CacheNeed, Part, lookup, register_mixer
+from .base import POSITION_ENCODINGS, ROTATION, CacheNeed, Part, lookup, register_mixer
 from .linear import Linear
 
 
@@ -26,35 +26,38 @@ class PagedAttention(Part):
         if spec.bias:
             raise Unsupported("attention with bias is not implemented")
         self.spec = spec
-        p = prefix + "self_attn."
+        p, nm = prefix, spec.names
         # q, k and v rows stacked: one projection, one read of the input
-        self.qkv = Linear(torch.cat([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
-                                     tensors[p + "v_proj.weight"]], dim=0).contiguous(), p + "qkv")
-        self.out = Linear(tensors[p + "o_proj.weight"], p + "o_proj")
-        self.q_norm_w = tensors[p + "q_norm.weight"] if spec.qk_norm else None
-        self.k_norm_w = tensors[p + "k_norm.weight"] if spec.qk_norm else None
+        self.qkv = Linear(torch.cat([tensors[p + nm.q], tensors[p + nm.k], tensors[p + nm.v]],
+                                    dim=0).contiguous(), p + "qkv")
+        self.out = Linear(tensors[p + nm.o], p + nm.o)
+        self.q_norm_w = tensors[p + nm.q_norm] if spec.qk_norm else None
+        self.k_norm_w = tensors[p + nm.k_norm] if spec.qk_norm else None
         self.eps = spec.qk_norm.eps if spec.qk_norm else 1.0
         self.position = None
         if spec.position is not None:
             self.position = lookup(POSITION_ENCODINGS, spec.position.kind, "position encoding")(
                 spec.position, mctx)
+            if getattr(self.position, "applies", ROTATION) != ROTATION:
+                raise Unsupported(f"position encoding {spec.position.kind!r} acts on "
+                                  f"{self.position.applies!r}; this attention applies rotations of q and k only")
         self.options = mctx.options
 
     @classmethod
     def tensor_decls(cls, spec: AttentionSpec, prefix: str) -> List[TensorDecl]:
-        p = prefix + "self_attn."
+        p, nm = prefix, spec.names
         qd, kvd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
-        decls = [TensorDecl(p + "q_proj.weight", (qd, spec.hidden_size), MATRIX),
-                 TensorDecl(p + "k_proj.weight", (kvd, spec.hidden_size), MATRIX),
-                 TensorDecl(p + "v_proj.weight", (kvd, spec.hidden_size), MATRIX),
-                 TensorDecl(p + "o_proj.weight", (spec.hidden_size, qd), MATRIX)]
+        decls = [TensorDecl(p + nm.q, (qd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + nm.k, (kvd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + nm.v, (kvd, spec.hidden_size), MATRIX),
+                 TensorDecl(p + nm.o, (spec.hidden_size, qd), MATRIX)]
         if spec.qk_norm:
-            decls += [TensorDecl(p + "q_norm.weight", (spec.head_dim,), VECTOR),
-                      TensorDecl(p + "k_norm.weight", (spec.head_dim,), VECTOR)]
+            decls += [TensorDecl(p + nm.q_norm, (spec.head_dim,), VECTOR),
+                      TensorDecl(p + nm.k_norm, (spec.head_dim,), VECTOR)]
         return decls
 
-    def cache_need(self) -> CacheNeed:
-        s = self.spec
+    @classmethod
+    def cache_need_of(cls, s: AttentionSpec) -> CacheNeed:
         return CacheNeed(PAGED_WINDOW if s.window else PAGED_ALL, s.kv_heads, s.head_dim, s.window)
 
     def can_fuse(self, ctx) -> bool:
@@ -76,21 +79,18 @@ class PagedAttention(Part):
         s = self.spec
         T = qkv.shape[0]
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
-        if self.position is not None:
-            cos, sin = self.position.tables(ctx)
-            half = self.position.half
-        else:
-            cos = sin = None
-            half = 0
+        # how the encoding turns q and k is the encoding's to say (pairing, rotary fraction): the kernels take it
+        rot = self.position.rotation(ctx) if self.position is not None else None
         attended = ctx.workspace.get("attn.out", T, s.heads * s.head_dim, ctx.dtype)
         if ops.attention_from_projection(ctx, qkv, k_pool, v_pool, attended, ctx.block_tables[group], self.q_norm_w,
-                                         self.k_norm_w, self.eps, cos, sin, half, run_step.writes_cache, s.heads,
+                                         self.k_norm_w, self.eps, rot, run_step.writes_cache, s.heads,
                                          s.kv_heads, s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0):
             return attended
         q = ctx.workspace.get("attn.q", T, s.heads * s.head_dim, ctx.dtype)
-        ops.qk_norm_rope_append(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, self.eps, cos, sin,
-                                ctx.kv_slot[group], s.heads, s.kv_heads, s.head_dim, half,
-                                write_kv=run_step.writes_cache)
+        ops.qk_norm_rope_append(qkv, q, k_pool, v_pool, self.q_norm_w, self.k_norm_w, self.eps,
+                                rot.cos if rot else None, rot.sin if rot else None, ctx.kv_slot[group], s.heads,
+                                s.kv_heads, s.head_dim, rot.pairs if rot else 0, write_kv=run_step.writes_cache,
+                                interleaved=bool(rot and rot.interleaved))
         ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
                             s.head_dim, k_pool.shape[2], s.softmax_scale, s.window or 0)
         return attended

@@ -4,7 +4,8 @@ A part is built from its own specification (sizes and constants as fields) and
 the tensors it declared; it never learns which model it is in.  Five kinds:
 
 * Norm:             ``apply(residual, delta, out, rows=None)``
-* PositionEncoding: ``prepare(ctx)`` once per step; a mixer asks it for its tables
+* PositionEncoding: says how it is applied (``applies``): ``rotation(ctx)`` gives a mixer the step's
+                    rotation of q and k; ``add_to_embedding(ctx, residual)`` adds to the embedded tokens
 * Mixer:            ``cache_need()``, ``forward(ctx, x, run_step) -> [T, hidden]``
 * FeedForward:      ``forward(ctx, x) -> [T, hidden]``
 * Block:            ``forward(ctx, residual, pending, run_step) -> pending``
@@ -95,6 +96,16 @@ class Workspace:
         return buf[:rows]
 
 
+# Words of a step's status buffer (int32, on the device; zero = fine).  The engine reads them back
+# with the step's result and fails the step if one is set.
+FAULT_WAIT, FAULT_TOKEN, FAULT_ACTIVATION, FAULT_LOGITS = 0, 1, 2, 3
+STATUS_WORDS = 8
+FAULT_NAMES = {FAULT_WAIT: "a kernel gave up on a bounded wait",
+               FAULT_TOKEN: "a token id outside the embedding table",
+               FAULT_ACTIVATION: "a non-finite activation",
+               FAULT_LOGITS: "a non-finite logit"}
+
+
 @dataclass
 class StepContext:
     """The ragged batch of one step, flattened, on the device.
@@ -123,6 +134,22 @@ class StepContext:
     max_kv_len: int = 1
     kv_bound: int = 1                         # an upper bound of max_kv_len that kernels may size their grids by
     options: dict = field(default_factory=dict)   # the engine's options, for parts that have switches
+    status: Optional[torch.Tensor] = None     # int32 [STATUS_WORDS]: the step's fault words (None: the model's own)
+
+
+@dataclass
+class Rotation:
+    """How a rotary position encoding turns the q and k heads of this step's tokens: the first
+    2 * pairs elements of a head are rotated pair by pair, pair i by the angle whose cosine and sine
+    are cos[t, i] and sin[t, i]; the rest of the head passes unchanged (a rotary fraction below one).
+    The partners of pair i are the elements (i, i + pairs), or (2i, 2i + 1) when interleaved."""
+    cos: torch.Tensor            # float32 [T, pairs]
+    sin: torch.Tensor
+    pairs: int
+    interleaved: bool = False
+
+
+ROTATION, EMBEDDING = "rotation", "embedding"      # PositionEncoding.applies
 
 
 @dataclass
@@ -143,7 +170,14 @@ class NormedInput:
 
 
 class Part:
-    """Common behaviour: a part declares its tensors before it is built."""
+    """Common behaviour: a part declares its tensors before it is built.
+
+    A position encoding also says where it acts, in the class attribute ``applies``:
+    ROTATION -- mixers call ``rotation(ctx) -> Rotation`` and turn q and k with it;
+    EMBEDDING -- the model calls ``add_to_embedding(ctx, residual)`` once, after the token rows are
+    gathered into the float32 residual stream (absolute and learned encodings).  An encoding that
+    acts on the attention scores would need mixers whose kernels take a bias: none here does, and
+    the attention part refuses such an encoding when it is built."""
 
     # Whether the kernels a forward launches depend on the step's device tensors only (block tables,
     # positions, slots), not on its host lists.  Decode-only steps of a model whose parts all say so
@@ -154,3 +188,12 @@ class Part:
     @classmethod
     def tensor_decls(cls, spec, prefix: str) -> List[TensorDecl]:
         return []
+
+    # A mixer says what it needs from the cache manager from its specification alone, so that the
+    # needs of a model are known before any weight is read (``inspect``, admission arithmetic).
+    @classmethod
+    def cache_need_of(cls, spec) -> "CacheNeed":
+        return CacheNeed("none")
+
+    def cache_need(self) -> "CacheNeed":
+        return type(self).cache_need_of(self.spec)

@@ -16,15 +16,13 @@ from .base import FEED_FORWARDS, MIXERS, NORMS, Part, lookup, register_block
 
 @register_block("pre_norm")
 class PreNormBlock(Part):
-    MIXER_NORM, FF_NORM = "input_layernorm.weight", "post_attention_layernorm.weight"
-
     def __init__(self, spec: LayerSpec, tensors: dict, mctx):
         p = spec.weight_prefix
         self.spec = spec
-        self.mixer_norm = lookup(NORMS, spec.mixer_norm.kind, "norm")(spec.mixer_norm, p + self.MIXER_NORM,
+        self.mixer_norm = lookup(NORMS, spec.mixer_norm.kind, "norm")(spec.mixer_norm, p + spec.mixer_norm_name,
                                                                       tensors, mctx)
         self.ff_norm = lookup(NORMS, spec.feed_forward_norm.kind, "norm")(spec.feed_forward_norm,
-                                                                          p + self.FF_NORM, tensors, mctx)
+                                                                          p + spec.feed_forward_norm_name, tensors, mctx)
         self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer, p, tensors, mctx)
         self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
             spec.feed_forward, p, tensors, mctx)
@@ -35,10 +33,10 @@ class PreNormBlock(Part):
     @classmethod
     def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
         p = spec.weight_prefix
-        return (lookup(NORMS, spec.mixer_norm.kind, "norm").tensor_decls(spec.mixer_norm, p + cls.MIXER_NORM)
+        return (lookup(NORMS, spec.mixer_norm.kind, "norm").tensor_decls(spec.mixer_norm, p + spec.mixer_norm_name)
                 + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_decls(spec.mixer, p)
                 + lookup(NORMS, spec.feed_forward_norm.kind, "norm").tensor_decls(spec.feed_forward_norm,
-                                                                                 p + cls.FF_NORM)
+                                                                                 p + spec.feed_forward_norm_name)
                 + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(
                     spec.feed_forward, p))
 

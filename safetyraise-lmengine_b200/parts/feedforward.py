@@ -20,8 +20,8 @@ class GatedDense(Part):
         if spec.activation != "silu":
             raise Unsupported(f"activation {spec.activation!r} is not implemented")
         self.spec = spec
-        p = prefix + "mlp."
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        p, nm = prefix, spec.names
+        gate, up = tensors[p + nm.gate], tensors[p + nm.up]
         I, H = gate.shape
         # One projection for gate and up.  For the tensor-core kernels the rows are interleaved in
         # blocks of 16 (8 gate rows, then the 8 up rows of the same features) so that the product's
@@ -34,14 +34,14 @@ class GatedDense(Part):
         else:
             w = torch.cat([gate, up], dim=0)
         self.gate_up = Linear(w.contiguous(), p + "gate_up")
-        self.down = Linear(tensors[p + "down_proj.weight"], p + "down_proj")
+        self.down = Linear(tensors[p + nm.down], p + nm.down)
 
     @classmethod
     def tensor_decls(cls, spec: FeedForwardSpec, prefix: str) -> List[TensorDecl]:
-        p = prefix + "mlp."
-        return [TensorDecl(p + "gate_proj.weight", (spec.intermediate_size, spec.hidden_size), MATRIX),
-                TensorDecl(p + "up_proj.weight", (spec.intermediate_size, spec.hidden_size), MATRIX),
-                TensorDecl(p + "down_proj.weight", (spec.hidden_size, spec.intermediate_size), MATRIX)]
+        p, nm = prefix, spec.names
+        return [TensorDecl(p + nm.gate, (spec.intermediate_size, spec.hidden_size), MATRIX),
+                TensorDecl(p + nm.up, (spec.intermediate_size, spec.hidden_size), MATRIX),
+                TensorDecl(p + nm.down, (spec.hidden_size, spec.intermediate_size), MATRIX)]
 
     def can_fuse(self, ctx) -> bool:
         return self.fused and self.gate_up.can_fuse(ctx, ctx.T) and self.down.can_fuse(ctx, ctx.T)

@@ -10,22 +10,24 @@ import torch
 
 from ..config.spec import PositionSpec
 from ..kernels import ops
-from .base import Part, register_position_encoding
+from .base import ROTATION, Part, Rotation, register_position_encoding
 
 
 @register_position_encoding("rotary_half")
 class RotaryHalf(Part):
+    applies = ROTATION
+
     def __init__(self, spec: PositionSpec, mctx):
         self.spec = spec
         self.half = spec.rotary_dim // 2
         self.key = ("rotary_half", spec.theta, spec.rotary_dim)
 
-    def tables(self, ctx):
-        """(cos, sin) float32 [T, rotary_dim/2] for the tokens of this step."""
+    def rotation(self, ctx) -> Rotation:
+        """The rotation of this step's tokens: cos / sin float32 [T, rotary_dim/2], half-split pairs."""
         got = ctx.tables.get(self.key)
         if got is None:
             cos = ctx.workspace.get(f"rope.cos.{self.spec.theta}", ctx.T, self.half, torch.float32)
             sin = ctx.workspace.get(f"rope.sin.{self.spec.theta}", ctx.T, self.half, torch.float32)
             ops.rope_table(ctx.positions, cos, sin, self.spec.theta, self.spec.rotary_dim)
-            got = ctx.tables[self.key] = (cos, sin)
+            got = ctx.tables[self.key] = Rotation(cos, sin, self.half, interleaved=False)
         return got

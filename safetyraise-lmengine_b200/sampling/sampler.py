@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from ..parts.base import FAULT_LOGITS, STATUS_WORDS
 from .params import SamplingParams
 
 _MASK = (1 << 64) - 1
@@ -39,19 +40,37 @@ def fresh_seed() -> int:
 
 
 class Sampler:
-    def __init__(self, device, vocab_size: int, max_rows: int = 64):
+    """``status``: an engine's status buffer (int32: STATUS_WORDS fault words, then room for one token per
+    request).  With it the sampled tokens are written behind the fault words and one read-back
+    fetches both; a non-finite logit raises the word FAULT_LOGITS (src/frontend/sampling.rs:97-99).
+    Without it the sampler keeps words of its own."""
+
+    def __init__(self, device, vocab_size: int, max_rows: int = 64, status: torch.Tensor = None):
         self.device, self.vocab = device, vocab_size
-        self.bad = torch.zeros(1, dtype=torch.int32, device=device)
+        self._shared = status is not None
+        self._status = status
+        if status is None:
+            self._status = torch.zeros(STATUS_WORDS + max_rows, dtype=torch.int32, device=device)
+        self._words = STATUS_WORDS
+        self.bad = self._status[FAULT_LOGITS:FAULT_LOGITS + 1]
+        self.last_words = [0] * STATUS_WORDS      # the fault words as the last collect() read them
         self._cap = 0
         self._grow(max_rows)
 
     def _grow(self, rows: int):
         if rows <= self._cap:
             return
+        if self._words + rows > self._status.numel():
+            if self._shared:
+                raise ValueError(f"{rows} rows to sample exceed the engine's {self._status.numel() - self._words}")
+            old = self._status
+            self._status = torch.zeros(self._words + rows, dtype=torch.int32, device=self.device)
+            self._status[:self._words].copy_(old[:self._words])
+            self.bad = self._status[FAULT_LOGITS:FAULT_LOGITS + 1]
         self._cap = rows
         self._host = torch.empty(5 * rows, dtype=torch.float32, pin_memory=True)
         self._dev = torch.empty(5 * rows, dtype=torch.float32, device=self.device)
-        self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        self._out = self._status[self._words:self._words + rows]
         self._scratch = None               # [rows, vocab] float32, made when a row is first sampled
         if not hasattr(self, "_hist_host"):
             self._hist_host = self._hist_dev = None
@@ -62,8 +81,15 @@ class Sampler:
         return self.collect(self.launch(logits, params, seeds, indices, histories))
 
     def collect(self, n: int) -> List[int]:
-        """The tokens of the last launch(): waits for the device and reads them back."""
-        return self._out[:n].tolist() if n else []
+        """The tokens of the last launch(): waits for the device and reads them back, the fault words
+        with them (``last_words``; the caller decides what a raised word means)."""
+        got = self._status[:self._words + n].tolist()
+        self.last_words = got[:self._words]
+        return got[self._words:]
+
+    def clear_words(self) -> None:
+        self._status[:self._words].zero_()
+        self.last_words = [0] * self._words
 
     def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int], histories: Sequence[Sequence[int]]) -> int:

@@ -79,6 +79,29 @@ def load_tensors(source, decls: Sequence[TensorDecl], compute_dtype: torch.dtype
     return out
 
 
+class PrefixedSource:
+    """A weight source seen under other names: a stored name that begins with ``stored_prefix`` is
+    offered with ``prefix`` in its place; every other name is offered as it is."""
+
+    def __init__(self, source, prefix: str, stored_prefix: str):
+        self._source = source
+        self._stored = {}
+        for n in source.names():
+            shown = prefix + n[len(stored_prefix):] if n.startswith(stored_prefix) else n
+            if shown in self._stored:
+                raise WeightError(f"tensors {self._stored[shown]} and {n} would both be read as {shown}")
+            self._stored[shown] = n
+
+    def names(self):
+        return self._stored.keys()
+
+    def meta(self, name):
+        return self._source.meta(self._stored[name])
+
+    def get(self, name):
+        return self._source.get(self._stored[name])
+
+
 def logical_bytes(source) -> Tuple[int, int]:
     """(tensor count, total stored bytes), as ``inspect`` reports them (src/cli.rs:100-124)."""
     count = total = 0

@@ -43,14 +43,37 @@ TINY_D = {
     "head_dim": 80, "intermediate_size": 132, "vocab_size": 257, "rope_theta": 10000.0,
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 192,
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# E and F: more than 16 query heads per KV head (32 and 20), where a decode step no longer fits the
+# 16 rows of the keys-split attention kernels; head sizes 64 and 128.  G: half of every head rotated
+# (partial_rotary_factor 0.5), head size 64, so decode steps leave the kernel that rotates whole heads.
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 32, "num_key_value_heads": 1,
+    "head_dim": 64, "intermediate_size": 144, "vocab_size": 300, "rope_theta": 100000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 160,
+}
+TINY_F = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 1, "hidden_size": 72, "num_attention_heads": 40, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 96, "vocab_size": 200, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 160,
+}
+TINY_G = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 160, "vocab_size": 280, "rope_theta": 10000.0,
+    "partial_rotary_factor": 0.5,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 160,
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4),
+        "F": (TINY_F, 5), "G": (TINY_G, 6)}
 
 
-def make_folder(tmp_path_factory_or_dir, config, seed, name="model"):
+def make_folder(tmp_path_factory_or_dir, config, seed, name="model", store="BF16"):
     from safetyraise_lmengine_b200.weights.random_init import write_model_folder
     base = tmp_path_factory_or_dir
     out = str(base.mktemp(name)) if hasattr(base, "mktemp") else os.path.join(str(base), name)
-    return write_model_folder(config, seed, out)
+    return write_model_folder(config, seed, out, store=store)
 
 
 @pytest.fixture(scope="session")
@@ -63,7 +86,16 @@ def folder_b(tmp_path_factory):
     return make_folder(tmp_path_factory, TINY_B, 1, "tiny_b")
 
 
-@pytest.fixture(scope="session", params=["A", "B", "C", "D"])
+@pytest.fixture(scope="session", params=["A", "B", "C", "D", "E", "F", "G"])
 def tiny_folder(request, tmp_path_factory):
     cfg, seed = TINY[request.param]
     return request.param, make_folder(tmp_path_factory, cfg, seed, "tiny_" + request.param.lower())
+
+
+# Folders whose matrices are stored in other types than bfloat16 (values not representable in it):
+# config B (untied head) as F32 and config A (tied) as F16.
+@pytest.fixture(scope="session", params=["B-F32", "A-F16"])
+def stored_folder(request, tmp_path_factory):
+    name, store = request.param.split("-")
+    cfg, seed = TINY[name]
+    return name, store, make_folder(tmp_path_factory, cfg, seed + 20, "stored_" + request.param.lower(), store=store)

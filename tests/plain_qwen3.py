@@ -148,14 +148,15 @@ def attention_part(n1, positions, w, prefix, cfg) -> np.ndarray:
     hd = cfg.get("head_dim", cfg["hidden_size"] // nq)
     eps = cfg.get("rms_norm_eps", 1e-6)
     theta = rope_theta(cfg)
+    rotary_dim = rotary_dim_of(cfg, hd)
     T = n1.shape[0]
     q = linear(n1, w[prefix + "q_proj.weight"]).reshape(T, nq, hd)
     k = linear(n1, w[prefix + "k_proj.weight"]).reshape(T, nkv, hd)
     v = linear(n1, w[prefix + "v_proj.weight"]).reshape(T, nkv, hd)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
-    q = rope(q, positions, theta, hd)
-    k = rope(k, positions, theta, hd)
+    q = rope(q, positions, theta, rotary_dim)
+    k = rope(k, positions, theta, rotary_dim)
     a = causal_attention(q, k, v).reshape(T, nq * hd)
     return linear(a, w[prefix + "o_proj.weight"])
 
@@ -185,6 +186,17 @@ def rope_theta(cfg) -> float:
         if isinstance(sub, dict) and "rope_theta" in sub:
             return float(sub["rope_theta"])
     return float(cfg.get("rope_theta", 1e6))
+
+
+def rotary_dim_of(cfg, head_dim: int) -> int:
+    """floor(head_dim * partial_rotary_factor), the factor looked up like rope_theta, default 1.
+    src/model/spec.rs:266-282; elements beyond it pass unrotated (src/model/math.rs:66-67, 93-95)."""
+    fraction = cfg.get("partial_rotary_factor", 1.0)
+    for key in ("rope_parameters", "rope_scaling"):
+        sub = cfg.get(key)
+        if isinstance(sub, dict) and "partial_rotary_factor" in sub:
+            fraction = sub["partial_rotary_factor"]
+    return int(head_dim * float(fraction))
 
 
 def model_logits(cfg: dict, w: dict, tokens, dtype=np.float64) -> np.ndarray:

@@ -85,13 +85,13 @@ def mixed_schedule(reqs, chunk=8):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_mixed_batches_with_page_reuse(tiny_folder, dtype):
+@pytest.mark.parametrize("page", [4, 16])
+def test_mixed_batches_with_page_reuse(tiny_folder, dtype, page):
     name, folder = tiny_folder
     cfg, _ = TINY[name]
     rng = np.random.default_rng(7)
     lens = [23, 9, 41, 30, 17, 55, 12, 38]
     reqs = {f"m{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(lens)}
-    page = 4
     # room for the four largest at once, far less than all eight: pages must be used again
     num_pages = sum(sorted((n + page - 1) // page for n in lens)[-4:])
     eng = build(folder, dtype, num_pages=num_pages, page_size=page)
@@ -103,6 +103,59 @@ def test_mixed_batches_with_page_reuse(tiny_folder, dtype):
     taken, reused = eng.cache.reuse_counts()
     assert reused > 0 and taken > num_pages
     assert eng.cache.audit() == 0 and eng.cache.free_pages() == num_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_folders_stored_as_f32_and_f16_through_the_cuttings(stored_folder, dtype):
+    """Matrices stored in 32 bits stay in 32 bits (in a bfloat16 engine they run the float32 product
+    between bfloat16 activations); matrices stored as F16 are widened for the float32 engine and
+    rounded to bfloat16 for the other.  Their values are not representable in bfloat16, so the float32
+    engine is shown weights that bfloat16 cannot hold."""
+    name, store, folder = stored_folder
+    eng = build(folder, dtype, num_pages=40, page_size=4)
+    w = eng.model.blocks[0].mixer.qkv.weight
+    assert w.dtype == (torch.float32 if store == "F32" or dtype == "float32" else torch.bfloat16)
+    if dtype == "float32":
+        assert not torch.equal(w, w.to(torch.bfloat16).float())            # more bits than bfloat16 holds
+    reqs = requests_for(name, seed=3)
+    long = {k: v for k, v in reqs.items() if len(v) >= 33}
+    for cut, which in ((cut_whole, reqs), (cut_bulk_tail, long), (cut_portions, {k: v for k, v in reqs.items() if len(v) >= 2})):
+        got = {}
+        for rid, toks in which.items():
+            got.update(replay(eng, cut(rid, toks)))
+        check_against_plain(got, folder, which, dtype)
+    cfg, _ = TINY[name]
+    rng = np.random.default_rng(17)
+    mixed = {f"m{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate([23, 9, 41, 30, 17, 38])}
+    tight = build(folder, dtype, num_pages=sum(sorted((n + 3) // 4 for n in (23, 9, 41, 30, 17, 38))[-4:]), page_size=4)
+    check_against_plain(replay(tight, mixed_schedule(mixed)), folder, mixed, dtype)
+    assert tight.cache.reuse_counts()[1] > 0 and tight.cache.audit() == 0
+
+
+@pytest.mark.parametrize("name", ["E", "F"])
+def test_decode_steps_with_large_head_groups_replay_graphs(name, tmp_path_factory):
+    """More than 16 query heads per KV head: a decode step runs the rows-split attention kernel, whose
+    work list must be on the device before a CUDA graph of the step is recorded.  The decoded tail of
+    32 tokens runs from the recorded graph and must agree with the plain implementation."""
+    from conftest import make_folder
+    cfg, seed = TINY[name]
+    folder = make_folder(tmp_path_factory, cfg, seed, "groups_" + name.lower())
+    eng = build(folder, "bfloat16")
+    assert eng.use_graphs
+    reqs = {k: v for k, v in requests_for(name).items() if len(v) >= 64}
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_bulk_tail(rid, toks, 32)))
+    check_against_plain(got, folder, reqs, "bfloat16")
+    assert eng.graph_replays >= 30 * len(reqs) - 4
+    # two requests decoding side by side, one graph for both
+    two = dict(list(requests_for(name, seed=1).items())[-2:])
+    steps = [{"entries": [(r, t[:40], list(range(40))) for r, t in two.items()]}]
+    steps += [{"entries": [(r, t[40 + i:41 + i], [0]) for r, t in two.items()]} for i in range(24)]
+    two = {r: t[:64] for r, t in two.items()}
+    before = eng.graph_replays
+    check_against_plain(replay(eng, steps), folder, two, "bfloat16")
+    assert eng.graph_replays >= before + 20
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

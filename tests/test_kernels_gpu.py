@@ -334,6 +334,66 @@ def test_gemm_tcgen05_persistent_forms(M, N, K, dealt, odt):
         assert torch.allclose(out3.float(), ref3, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nq, nkv, hd, rd", [(4, 2, 16, 16), (3, 1, 48, 20), (2, 2, 128, 128), (6, 2, 64, 32)])
+@pytest.mark.parametrize("dt", ACT)
+def test_qk_norm_rope_append_interleaved_pairs(nq, nkv, hd, rd, dt):
+    """Pairs (2i, 2i+1) of the first rd elements of a head, as other rotary encodings use them."""
+    g = torch.Generator(device=DEV).manual_seed(6)
+    T, pages, ps, eps = 9, 6, 4, 1e-6
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV, generator=g).to(dt)
+    qw = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)
+    kw = 1 + 0.1 * torch.randn(hd, device=DEV, generator=g)
+    pos = torch.tensor([0, 1, 2, 50, 51, 7, 8, 9, 300], dtype=torch.int32, device=DEV)
+    half = rd // 2
+    cos, sin = torch.empty(T, half, device=DEV), torch.empty(T, half, device=DEV)
+    ops().rope_table(pos, cos, sin, 1e4, rd)
+    slots = torch.randperm(pages * ps, device=DEV, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, nkv, ps, hd, device=DEV, dtype=dt)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(T, nq * hd, device=DEV, dtype=dt)
+    ops().qk_norm_rope_append(qkv, q, kc, vc, qw, kw, eps, cos, sin, slots, nq, nkv, hd, half, interleaved=True)
+
+    def ref(x, w):
+        x = x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+        out = x.clone()
+        e, o = x[..., 0:rd:2], x[..., 1:rd:2]
+        c, sn = cos[:, None, :], sin[:, None, :]
+        out[..., 0:rd:2] = e * c - o * sn
+        out[..., 1:rd:2] = o * c + e * sn
+        return out
+
+    x = qkv.float().view(T, nq + 2 * nkv, hd)
+    assert torch.allclose(q.float().view(T, nq, hd), ref(x[:, :nq], qw), **tol(dt))
+    kflat = kc.float().permute(0, 2, 1, 3).reshape(pages * ps, nkv, hd)
+    assert torch.allclose(kflat[slots.long()], ref(x[:, nq:nq + nkv], kw), **tol(dt))
+    if rd == hd and hd >= 16:       # and it is not the half-split rotation
+        assert not torch.allclose(q.float().view(T, nq, hd), ref_norm_rope(x[:, :nq], qw, eps, cos, sin, half), **tol(dt))
+
+
+def test_gemm_tcgen05_tensor_maps_survive_the_emptying_of_their_cache():
+    """The cache of tensor maps is emptied when it is full.  A product looks up the weight's map, then
+    the activations' map: when the second lookup empties the cache, the first map must still be whole
+    (it is copied out under the lock, never pointed to)."""
+    import ctypes as C
+    lib = ops().lib
+    limit = C.c_int(0)
+    lib.srlm_gemm_tcgen05_map_cache(C.byref(limit))
+    g = torch.Generator(device=DEV).manual_seed(8)
+    N, K = 128, 64
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    big = (torch.randn(limit.value + 40, K, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    out = torch.empty(9, N, device=DEV, dtype=torch.float32)
+    emptied = 0
+    for i in range(limit.value + 30):                                # every start row is a new key for the activations
+        before = lib.srlm_gemm_tcgen05_map_cache(None)
+        ops().gemm_tn_tcgen05(big[i:i + 9], w, out)
+        if lib.srlm_gemm_tcgen05_map_cache(None) < before:           # this call emptied the cache between its lookups
+            emptied += 1
+            assert torch.allclose(out, big[i:i + 9].float() @ w.float().t(), rtol=1e-3, atol=1e-3), i
+    assert emptied >= 1
+    assert ops().gemm_error_flag(torch.device(DEV)) == 0
+
+
 def test_gemm_tcgen05_finds_each_k_and_row():
     """Identity-like operands: a misplaced row, column or k block shows as a wrong integer."""
     K, N, M = 256, 256, 40

@@ -88,8 +88,10 @@ def test_rotary_part(theta, hd):
     from safetyraise_lmengine_b200.parts.position import RotaryHalf
     part = RotaryHalf(PositionSpec("rotary_half", theta, hd, hd), mctx(torch.float32))
     ctx = make_ctx(torch.float32, 50)
-    cos, sin = part.tables(ctx)
-    assert part.tables(ctx)[0] is cos                      # made once per step
+    rot = part.rotation(ctx)
+    cos, sin = rot.cos, rot.sin
+    assert part.rotation(ctx) is rot and part.applies == "rotation"       # made once per step
+    assert rot.pairs == hd // 2 and not rot.interleaved
     x = np.random.default_rng(0).normal(size=(50, 3, hd))
     got = x.copy()
     c, s = cos.cpu().double().numpy()[:, None, :], sin.cpu().double().numpy()[:, None, :]

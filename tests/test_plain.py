@@ -29,6 +29,20 @@ def test_partial_rope_keeps_the_tail():
     assert list(y[0, 0, 2:]) == [7.0, 9.0]
 
 
+def test_rope_pairs_are_half_split():
+    # src/model/math.rs:91-95: (left, right) = (head[i], head[i + half]) with half = rotary_dim / 2.
+    # rotary_dim 4 of head_dim 6, theta 1 (every angle equals the position), position 1: the pairs
+    # are (0, 2) and (1, 3), not (0, 1) and (2, 3); elements 4 and 5 pass
+    x = np.array([[[1.0, 2.0, 3.0, 4.0, 5.0, 6.0]]])
+    y = P.rope(x, np.array([1]), 1.0, 4)[0, 0]
+    c, s = math.cos(1.0), math.sin(1.0)
+    want = [1 * c - 3 * s, 2 * c - 4 * s, 3 * c + 1 * s, 4 * c + 2 * s, 5.0, 6.0]
+    assert np.allclose(y, want, rtol=0, atol=1e-12)
+    assert P.rotary_dim_of({"partial_rotary_factor": 0.5}, 64) == 32
+    assert P.rotary_dim_of({"rope_parameters": {"partial_rotary_factor": 0.25}, "partial_rotary_factor": 0.5}, 64) == 16
+    assert P.rotary_dim_of({}, 48) == 48
+
+
 def test_rms_norm_and_silu():
     x = np.array([[3.0, 4.0]])
     y = P.rms_norm(x, np.array([1.0, 2.0]), 1e-6)
