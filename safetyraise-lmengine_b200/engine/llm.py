@@ -83,6 +83,7 @@ class LLM:
         self._ids = itertools.count(1)
         self.failed = self.cancelled = 0
         self._prepared = None          # (plan, PreparedStep, open token places) of a step laid out ahead
+        self.last_step: Optional[dict] = None   # what the last step ran: {"starts": [...], "counts": [...]} per entry
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -94,6 +95,18 @@ class LLM:
             setattr(config, k, v)
         config.validate()
         engine = Engine.from_folder(model_path, dtype=config.dtype, device=config.device,
+                                    page_size=config.page_size, num_pages=config.num_pages,
+                                    max_requests=config.max_active, max_batch_tokens=config.max_batch_tokens,
+                                    max_context=config.max_context)
+        return cls(engine, config)
+
+    @classmethod
+    def from_source(cls, config_json: dict, source, config: Optional[EngineConfig] = None) -> "LLM":
+        """A model from its config.json (as a dict) and any weight source, for instance
+        ``weights.random_init.RandomWeights``: the random-weights mode."""
+        config = config or EngineConfig()
+        config.validate()
+        engine = Engine.from_source(config_json, source, dtype=config.dtype, device=config.device,
                                     page_size=config.page_size, num_pages=config.num_pages,
                                     max_requests=config.max_active, max_batch_tokens=config.max_batch_tokens,
                                     max_context=config.max_context)
@@ -232,6 +245,7 @@ class LLM:
         except EngineError as e:
             self._fail_plan(plan, e)
             return True
+        self.last_step = {"starts": [p.start for p in plan], "counts": [p.count for p in plan]}
         sampled = [p for p in plan if p.want_logits]
         states = [self._live[p.request_id] for p in sampled]
         rows = self.sampler.launch(

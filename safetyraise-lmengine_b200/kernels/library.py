@@ -80,8 +80,31 @@ class KernelLibrary:
         """Programmatic dependent launch between the kernels of a step (on by default)."""
         self.lib.srlm_set_pdl(C.c_int(1 if on else 0))
 
+    def begin_timing(self) -> None:
+        """From now on every launch is followed by a CUDA event; ``end_timing`` turns the gaps between
+        consecutive events into a table.  Kernels of one stream run one after the other, so the gap
+        before a launch's event is that kernel's time (with its launch gap; no overlap between kernels
+        is possible while this is on: use it on eager steps, for shares, not for absolutes)."""
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        self._timing = [("", start)]
+
+    def end_timing(self) -> dict:
+        """{kernel name: (launches, milliseconds)} since begin_timing (waits for the device)."""
+        marks, self._timing = getattr(self, "_timing", None) or [], None
+        torch.cuda.synchronize()
+        table: dict = {}
+        for (_, before), (name, after) in zip(marks, marks[1:]):
+            n, ms = table.get(name, (0, 0.0))
+            table[name] = (n + 1, ms + before.elapsed_time(after))
+        return table
+
     def _check(self, status: int, what: str):
         self.launches += 1
+        if getattr(self, "_timing", None) is not None and status == 0:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._timing.append((what, ev))
         if status != 0:
             msg = self.lib.srlm_last_error().decode(errors="replace")
             if status < 0:

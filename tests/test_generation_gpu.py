@@ -281,6 +281,26 @@ def test_cli_inspect_run_benchmark(folder_a, tmp_path):
     assert out.returncode == 0, out.stderr
     b = json.loads(out.stdout)
     assert len(b["runs"]) == 2 and b["runs"][0]["completion_tokens"] == 5
+    groups = info["cache_groups"]
+    assert len(groups) == 1 and groups[0]["kind"] == "paged_all" and groups[0]["entries"] == 2
+    # the random-weights mode: config.json alone; the tensors are functions of (seed, name), so a folder
+    # written from the same seed holds the same model
+    from safetyraise_lmengine_b200.weights.random_init import write_model_folder
+    cj = tmp_path / "model_config.json"
+    cj.write_text(json.dumps(TINY["B"][0]))
+    out = run_cli("inspect", "--random-weights", "77", "--config-json", str(cj), "--context", "32", "--dtype", "float32")
+    assert out.returncode == 0, out.stderr
+    assert json.loads(out.stdout)["tensors"] == 3 * 11 + 3
+    eng_only = tmp_path / "engine_only.json"
+    eng_only.write_text(json.dumps({"engine": {"max_context": 128, "max_active": 2, "page_size": 4, "num_pages": 40,
+                                               "dtype": "float32", "max_batch_tokens": 32}}))
+    out = run_cli("run", "--random-weights", "77", "--config-json", str(cj), "--config", str(eng_only),
+                  "--request", str(req))
+    assert out.returncode == 0, out.stderr
+    cfgd, w = P.read_model_folder(write_model_folder(TINY["B"][0], 77, str(tmp_path / "same_seed")))
+    assert json.loads(out.stdout)["tokens"] == P.greedy_generate(cfgd, w, prompt, 5)
+    out = run_cli("run", "--random-weights", "77", "--request", str(req))
+    assert out.returncode == 2 and "go together" in out.stderr
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps({"model_path": folder_a, "engine": {"no_such_option": 1}}))
     out = run_cli("run", "--config", str(bad), "--request", str(req))

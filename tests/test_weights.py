@@ -139,3 +139,52 @@ def test_sharded_folder(tmp_path):
         {"weight_map": {"a": "../s1.safetensors"}}))
     with pytest.raises(WeightError):
         WeightFolder(str(tmp_path))
+
+
+def _renamed_folder(tmp_path, config, seed):
+    """A folder whose text model is stored as model.language_model.* (the output head keeps its name)."""
+    spec = spec_from_config(config)
+    src = RandomWeights(tensor_decls(spec), seed)
+    tensors = {}
+    for n in src.names():
+        stored = "model.language_model." + n[len("model."):] if n.startswith("model.") else n
+        tensors[stored] = src.get(n)
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    return str(tmp_path), src
+
+
+def test_language_model_prefix_is_read_as_the_plain_names(tmp_path):
+    """src/model/native.rs:156-165: model.language_model.embed_tokens.weight present -> that prefix."""
+    from conftest import TINY_B
+    from safetyraise_lmengine_b200.config.registry import architecture_of
+    folder, src = _renamed_folder(tmp_path, TINY_B, 4)
+    arch = architecture_of(TINY_B)
+    raw = WeightFolder(folder)
+    assert "model.language_model.layers.2.mlp.down_proj.weight" in set(raw.names()) and "lm_head.weight" in set(raw.names())
+    decls = tensor_decls(arch.read_spec(TINY_B))
+    with pytest.raises(WeightError):                                 # as stored, nothing matches
+        check_against(decls, {n: raw.meta(n)[1] for n in raw.names()})
+    seen = arch.source_for(raw)
+    check_against(decls, {n: seen.meta(n)[1] for n in seen.names()})
+    t = load_tensors(seen, decls, torch.bfloat16, "cpu")
+    assert torch.equal(t["model.layers.2.mlp.down_proj.weight"], src.get("model.layers.2.mlp.down_proj.weight"))
+    assert torch.equal(t["lm_head.weight"], src.get("lm_head.weight"))
+    # a folder under the plain names passes through unchanged
+    plain = RandomWeights(decls, 4)
+    assert arch.source_for(plain) is plain
+
+
+def test_stored_types_of_random_folders(tmp_path):
+    from conftest import TINY_A
+    from safetyraise_lmengine_b200.weights.random_init import write_model_folder
+    for store, dt in (("F32", torch.float32), ("F16", torch.float16), ("BF16", torch.bfloat16)):
+        folder = write_model_folder(TINY_A, 9, str(tmp_path / store), store=store)
+        w = WeightFolder(folder)
+        assert w.meta("model.layers.0.mlp.up_proj.weight")[0] == dt
+        assert w.meta("model.norm.weight")[0] == torch.float32
+    t = load_tensors(WeightFolder(str(tmp_path / "F32")), tensor_decls(spec_from_config(TINY_A)), torch.bfloat16, "cpu")
+    m = t["model.layers.0.mlp.up_proj.weight"]
+    assert m.dtype == torch.float32 and not torch.equal(m, m.to(torch.bfloat16).float())
+    with pytest.raises(ValueError):
+        write_model_folder(TINY_A, 9, str(tmp_path / "x"), store="F8")
