@@ -17,9 +17,14 @@
  * process exits.
  *
  * Rules for the caller:
- *  - Sizes whose scratch need (65536 + splits * M * N * 4 bytes) exceeds the
- *    array are refused with a negative status and a message from
- *    srlm_last_error(); nothing is launched.
+ *  - With more than one split the partial sums lie in whole tiles of 128 weight
+ *    rows by bn tokens, bn being M rounded up to 16, 32, 64, 128 or 256 (the
+ *    smallest that holds M, else 256).  The scratch need is
+ *        65536 + splits * ceil(N / 128) * ceil(M / bn) * 128 * bn * 4  bytes
+ *    (up to twice splits * M * N * 4: M = 33 gives bn = 64), and there may be at
+ *    most 16384 tiles.  Sizes whose need exceeds the array are refused with a
+ *    negative status and a message from srlm_last_error(); nothing is launched.
+ *    A single split needs no scratch.
  *  - The first call on a device looks the array's device address up (and sets a
  *    kernel attribute).  Make that first call outside any stream capture.
  *  - All calls share the one array and it keeps the last call's contents; the

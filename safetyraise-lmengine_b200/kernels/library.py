@@ -46,14 +46,14 @@ class KernelLibrary:
         self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
         self.force_simt_attention = False
         self.force_tcgen05_gemm = False
-        import os
         # the weight-streaming kernel serves products of at most this many tokens and weight rows
-        self.skinny_max_tokens = int(os.environ.get("SRLM_SKINNY_TOKENS", "8"))
-        self.skinny_max_rows = int(os.environ.get("SRLM_SKINNY_ROWS", str(1 << 30)))
+        self.skinny_max_tokens = 8
+        self.skinny_max_rows = 1 << 30
         self.force_cp_async_decode = False
         self.cluster_decode_merge = True        # slices of decode attention merged in a thread-block cluster
         self.fuse_decode_attention = True       # decode: norm, rotation and append inside the attention kernel
         self.force_mma_sync_prefill = False
+        self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
 
     @property
     def lib(self):
@@ -270,16 +270,19 @@ class KernelLibrary:
         self._check(self.lib.srlm_gemm_tn_tcgen05(
             _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)), C.c_int(splits),
-            _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()), "gemm_tn_tcgen05")
+            _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()),
+            f"gemm_tn_tcgen05[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None else "gemm_tn_tcgen05")
 
     def gemm_dealt_tiles(self, M: int, N: int, K: int) -> int:
         """How many tiles of this product the persistent tensor-core kernel deals out by k-blocks
         (0: whole tiles only, or another kernel serves these sizes)."""
         return int(self.lib.srlm_gemm_tcgen05_dealt_tiles(C.c_int(M), C.c_int(N), C.c_int(K)))
 
-    def gemm_tn_skinny(self, a, w, out, swiglu8=False):
+    def gemm_tn_skinny(self, a, w, out, swiglu8=False, early=True):
         """out[M,N] = a[M,K] @ w[N,K]^T for M <= 16: the weight-streaming kernel of decode steps.
-        swiglu8: as in gemm_tn_tcgen05."""
+        swiglu8: as in gemm_tn_tcgen05.  early: the kernel may start under the tail of the kernel ahead
+        of it (it requests its first weights, then waits for that kernel's results); False for the
+        product that follows a mixer's own kernel, where that measured much slower."""
         M, K = a.shape
         N = w.shape[0]
         if (w.shape[1] != K or tuple(out.shape) != (M, N // 2 if swiglu8 else N) or a.dtype != torch.bfloat16
@@ -289,10 +292,11 @@ class KernelLibrary:
         self._check(self.lib.srlm_gemm_tn_skinny(
             _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(M), C.c_int(N), C.c_int(K),
             C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)), C.c_longlong(out.stride(0)),
-            C.c_int(int(swiglu8)), _stream()), "gemm_tn_skinny")
+            C.c_int(int(swiglu8)), C.c_int(int(early and self.early_launch)), _stream()),
+            f"gemm_tn_skinny[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None else "gemm_tn_skinny")
 
     def gemm_tn_skinny_fused(self, a, w, out=None, swiglu8=False, scale_parts=None, norm_width=0, eps=0.0,
-                             residual=None, next_w=None, xw_out=None, ss_out=None):
+                             residual=None, next_w=None, xw_out=None, ss_out=None, early=True):
         """The weight-streaming product (at most 8 tokens) fused with the norms around it.
 
         scale_parts [parts, 8] float32: ``a`` holds bf16(residual * norm weight); the product is scaled per
@@ -313,8 +317,10 @@ class KernelLibrary:
             C.c_longlong(out.stride(0) if out is not None else N), C.c_int(int(swiglu8)), _ptr(scale_parts),
             C.c_int(scale_parts.shape[0] if scale_parts is not None else 0), C.c_int(norm_width), C.c_float(eps),
             _ptr(residual), C.c_longlong(residual.stride(0) if residual is not None else 0), _ptr(next_w),
-            _ptr(xw_out), C.c_longlong(xw_out.stride(0) if xw_out is not None else 0), _ptr(ss_out), _stream()),
-            "gemm_tn_skinny_fused")
+            _ptr(xw_out), C.c_longlong(xw_out.stride(0) if xw_out is not None else 0), _ptr(ss_out),
+            C.c_int(int(early and self.early_launch)), _stream()),
+            f"gemm_tn_skinny_fused[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None
+            else "gemm_tn_skinny_fused")
 
     def can_fuse_norms(self, T: int, dtype, w) -> bool:
         """Whether a product of T tokens with this weight may take the norm fusions of the skinny kernel."""
@@ -327,15 +333,15 @@ class KernelLibrary:
         return (a_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
                 and w.shape[0] % 16 == 0 and not self.force_simt_gemm)
 
-    def gemm(self, a, w, out, swiglu8=False):
+    def gemm(self, a, w, out, swiglu8=False, early=True):
         """The product path's matrix product: picks the kernel for the dtypes and sizes.  bfloat16
         operands go to the tensor cores; float32 operands, and widths that TMA cannot address
-        (K not a multiple of 8), go to the float32 FMA kernel."""
+        (K not a multiple of 8), go to the float32 FMA kernel.  early: see gemm_tn_skinny."""
         if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
                 and not self.force_simt_gemm):
             if a.shape[0] <= self.skinny_max_tokens and w.shape[0] <= self.skinny_max_rows \
                     and not self.force_tcgen05_gemm:
-                self.gemm_tn_skinny(a, w, out, swiglu8)          # a few tokens: bound by streaming the weights
+                self.gemm_tn_skinny(a, w, out, swiglu8, early=early)   # a few tokens: bound by streaming the weights
             else:
                 self.gemm_tn_tcgen05(a, w, out, swiglu8=swiglu8)
         else:

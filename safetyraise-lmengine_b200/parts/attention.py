@@ -69,11 +69,11 @@ class PagedAttention(Part):
         qkv = ctx.workspace.get("attn.qkv", ctx.T, self.qkv.out_features, ctx.dtype)
         self.qkv.from_normed(ctx, nx, qkv)
         attended = self._attend(ctx, qkv, run_step)
-        return self.out.into_residual(ctx, attended, residual, next_norm, "a")
+        return self.out.into_residual(ctx, attended, residual, next_norm, "a", early=False)
 
     def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
         qkv = self.qkv(ctx, x, "attn.qkv")
-        return self.out(ctx, self._attend(ctx, qkv, run_step), "attn.proj")
+        return self.out(ctx, self._attend(ctx, qkv, run_step), "attn.proj", early=False)
 
     def _attend(self, ctx, qkv: torch.Tensor, run_step: RunStep) -> torch.Tensor:
         s = self.spec

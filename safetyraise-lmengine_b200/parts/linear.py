@@ -16,13 +16,16 @@ class Linear:
         self.weight, self.name = weight, name
         self.out_features, self.in_features = weight.shape
 
-    def __call__(self, ctx, x: torch.Tensor, out_name: str, out_dtype=None) -> torch.Tensor:
+    # ``early`` (everywhere below): whether the product's kernel may start under the tail of the kernel
+    # ahead of it.  A part passes False for a product that directly follows a kernel of its own with
+    # which that overlap measured slower (the attention kernel of a decode step).
+    def __call__(self, ctx, x: torch.Tensor, out_name: str, out_dtype=None, early: bool = True) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype
         out = ctx.workspace.get(out_name, x.shape[0], self.out_features, out_dtype)
-        self.into(ctx, x, out)
+        self.into(ctx, x, out, early=early)
         return out
 
-    def into(self, ctx, x: torch.Tensor, out: torch.Tensor) -> None:
+    def into(self, ctx, x: torch.Tensor, out: torch.Tensor, early: bool = True) -> None:
         w = self.weight
         if w.dtype == torch.float32 and x.dtype != torch.float32:
             x32 = ctx.workspace.get("linear.x32", x.shape[0], x.shape[1], torch.float32)
@@ -34,7 +37,7 @@ class Linear:
                 ops.gemm_tn_simt(x32, w, y32)
                 ops.cast(y32, out)
             return
-        ops.gemm(x, w, out)
+        ops.gemm(x, w, out, early=early)
 
     # ---- fused with the norms around it (decode steps of a few tokens) -------------------------
     def can_fuse(self, ctx, T: int) -> bool:
@@ -48,15 +51,16 @@ class Linear:
             ops.gemm_tn_skinny_fused(nx.xw, self.weight, out, swiglu8=swiglu8, scale_parts=nx.ss_parts,
                                      norm_width=nx.width, eps=nx.eps)
 
-    def into_residual(self, ctx, x: torch.Tensor, residual: torch.Tensor, next_norm, slot: str):
+    def into_residual(self, ctx, x: torch.Tensor, residual: torch.Tensor, next_norm, slot: str, early: bool = True):
         """residual += x . W^T in the product's epilogue.  With ``next_norm`` (an RMSNorm part) the same
         epilogue prepares the input of the part behind that norm and returns it as a NormedInput."""
         from .base import NormedInput
         if next_norm is None:
-            ops.gemm_tn_skinny_fused(x, self.weight, residual=residual)
+            ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, early=early)
             return None
         T, N = x.shape[0], self.out_features
         xw = ctx.workspace.get("fused.xw." + slot, T, N, ctx.dtype)
         ss = ctx.workspace.get("fused.ss." + slot, (N + 15) // 16, 8, torch.float32, reserve=0)
-        ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw, ss_out=ss)
+        ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw, ss_out=ss,
+                                 early=early)
         return NormedInput(xw, ss, next_norm.spec.size, next_norm.spec.eps)

@@ -14,6 +14,18 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_terminal_summary(terminalreporter):
+    """The largest engine-against-plain error of the run, per dtype: the tolerances in helpers.py are set
+    from these figures."""
+    try:
+        from helpers import TOL, WORST
+    except ImportError:
+        return
+    for dtype, (err, where) in sorted(WORST.items()):
+        terminalreporter.write_line(f"worst error against the plain implementation, {dtype}: {err:.3e} of the "
+                                    f"largest logit ({where}); tolerance {TOL[dtype]:.1e}")
+
+
 # Two tiny Qwen3 configurations that differ in every size and option.
 TINY_A = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",

@@ -7,8 +7,19 @@ import plain_qwen3
 
 # Largest |engine - plain| allowed, as a fraction of the largest |plain logit| compared.
 # float32: summation order is the only difference.  bfloat16: activations and the cache are
-# rounded to 8 bits of mantissa at every kernel boundary.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+# rounded to 8 bits of mantissa at every kernel boundary.  Twice the largest error any comparison of
+# the whole GPU suite has shown (5.4e-6 and 8.9e-3, both on one block at 14B / 32B layer sizes; the
+# run prints its own figures at its end).
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+# The largest error every comparison of this run has seen, per dtype (printed at the end of the run).
+WORST = {}
+
+
+def note_error(dtype: str, err: float, where: str = "") -> None:
+    if err > WORST.get(dtype, (0.0, ""))[0]:
+        WORST[dtype] = (err, where)
 
 
 def rel_err(got: np.ndarray, ref: np.ndarray) -> float:
@@ -93,4 +104,5 @@ def check_against_plain(got: dict, folder: str, requests: dict, dtype: str):
         assert bad.size == 0, (f"request {rid}: first wrong position {bad[0]} of {len(tokens)} "
                                f"(rel err {err[bad[0]]:.3e} > {TOL[dtype]:.0e}); wrong positions {bad[:20]}")
         worst = max(worst, float(err.max()))
+    note_error(dtype, worst, folder.rsplit("/", 1)[-1])
     return worst
