@@ -53,6 +53,8 @@ class KernelLibrary:
         self.cluster_decode_merge = True        # slices of decode attention merged in a thread-block cluster
         self.fuse_decode_attention = True       # decode: norm, rotation and append inside the attention kernel
         self.force_mma_sync_prefill = False
+        self.split_mixed_attention = True       # mixed steps: decoding requests to the keys-split kernel ...
+        self.split_mixed_min_blocks = None      # ... when they make this many blocks (None: one per SM)
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
 
     @property
@@ -446,21 +448,24 @@ class KernelLibrary:
         nsplit = -(-tiles * 64 // chunk)
         return nsplit, chunk
 
-    def _decode_plan(self, ctx, nkv, hd):
-        """(nsplit, kv_chunk, cluster, part_o, part_ml) for the TMA decode kernel on the batch of ctx."""
-        nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
+    def _decode_plan(self, ctx, nkv, hd, n_entries=None, kv_bound=None):
+        """(nsplit, kv_chunk, cluster, part_o, part_ml) for the TMA decode kernel on the batch of ctx, or on
+        ``n_entries`` of its entries whose keys number at most ``kv_bound``."""
+        n_entries = ctx.n_entries if n_entries is None else n_entries
+        kv_bound = ctx.kv_bound if kv_bound is None else kv_bound
+        nsplit, chunk = self.attention_split(n_entries, nkv, kv_bound)
         # Up to 8 slices merge inside a thread-block cluster, which saves the round trip through global
         # memory (6 to 8 us measured); more slices pay only when each of the 8 would have many more
         # tiles to walk (about 1 us a tile).
         cluster = False
         if self.cluster_decode_merge and nsplit > 1:
-            n8, chunk8 = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound, max_slices=8)
+            n8, chunk8 = self.attention_split(n_entries, nkv, kv_bound, max_slices=8)
             if chunk8 - chunk <= 7 * 64:
                 nsplit, chunk, cluster = n8, chunk8, True
         part_o = part_ml = None
         if nsplit > 1 and not cluster:
-            part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32, reserve=0)
-            part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2, torch.float32,
+            part_o = ctx.workspace.get("attn.part_o", n_entries * nkv * nsplit * 16, hd, torch.float32, reserve=0)
+            part_ml = ctx.workspace.get("attn.part_ml", n_entries * nkv * nsplit * 16, 2, torch.float32,
                                         reserve=0)
         return nsplit, chunk, cluster, part_o, part_ml
 
@@ -494,30 +499,71 @@ class KernelLibrary:
                                       nq, nkv, hd, page_size, scale, window)
             return
         g = nq // nkv
-        if ctx.max_q_len * g <= 16:
+
+        def keys_split(lo, hi):
+            """Entries lo..hi-1, each of at most 16 rows (tokens x heads per KV head): the kernels that split
+            the keys over blocks.  They index the step's q and out by the token offsets in cu_q, so a run of
+            entries is served by handing them the run's part of cu_q, kv_lens and the block table."""
+            n = hi - lo
+            whole = lo == 0 and hi == ctx.n_entries
+            bound = ctx.kv_bound if whole else max(ctx.host["kv_lens"][lo:hi])
+            cu, kvl, table = ctx.cu_q[lo:hi + 1], ctx.kv_lens[lo:hi], block_table[lo:hi]
             if self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size)) and not self.force_cp_async_decode:
-                nsplit, chunk, cluster, part_o, part_ml = self._decode_plan(ctx, nkv, hd)
-                self.paged_attention_decode_tma(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
-                                                ctx.n_entries, nq, nkv, hd, page_size, scale, window, chunk,
-                                                nsplit, part_o, part_ml, cluster=cluster)
+                nsplit, chunk, cluster, part_o, part_ml = self._decode_plan(ctx, nkv, hd, n, bound)
+                self.paged_attention_decode_tma(q, k_cache, v_cache, out, table, cu, kvl, n, nq, nkv, hd, page_size,
+                                                scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
                 return
-            nsplit, chunk = self.attention_split(ctx.n_entries, nkv, ctx.kv_bound)
+            nsplit, chunk = self.attention_split(n, nkv, bound)
             part_o = part_ml = None
             if nsplit > 1:
-                part_o = ctx.workspace.get("attn.part_o", ctx.n_entries * nkv * nsplit * 16, hd, torch.float32,
-                                           reserve=0)
-                part_ml = ctx.workspace.get("attn.part_ml", ctx.n_entries * nkv * nsplit * 16, 2, torch.float32,
-                                            reserve=0)
-            self.paged_attention_keys(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, ctx.n_entries,
-                                      nq, nkv, hd, page_size, scale, window, chunk, nsplit, part_o, part_ml)
+                part_o = ctx.workspace.get("attn.part_o", n * nkv * nsplit * 16, hd, torch.float32, reserve=0)
+                part_ml = ctx.workspace.get("attn.part_ml", n * nkv * nsplit * 16, 2, torch.float32, reserve=0)
+            self.paged_attention_keys(q, k_cache, v_cache, out, table, cu, kvl, n, nq, nkv, hd, page_size, scale,
+                                      window, chunk, nsplit, part_o, part_ml)
+
+        if ctx.max_q_len * g <= 16:
+            keys_split(0, ctx.n_entries)
             return
+        # A mixed step: decoding requests (a row or a few) beside portions of prompts.  A row tile of the
+        # rows-split kernels would be all but empty for a decoding request and would walk its keys alone,
+        # one block per KV head; so the decoding requests at the head and at the tail of the batch (the
+        # scheduler puts them first) go to the keys-split kernel, the rest to the rows-split one.
+        q_lens = ctx.host["q_lens"]
+        n = ctx.n_entries
+        head = 0
+        while head < n and q_lens[head] * g <= 16:
+            head += 1
+        tail = n
+        while tail > head and q_lens[tail - 1] * g <= 16:
+            tail -= 1
+        # Worth a launch of its own only when the decoding requests would fill a round of blocks of the
+        # rows-split kernel by themselves (one block per request and KV head) and their contexts are of
+        # similar length: the two launches run one after the other, and the keys-split one lasts as long
+        # as its longest request, while row tiles of all kinds share the SMs in one launch.  Measured at
+        # 8B / 14B sizes: 31 decoding requests of 1,500 tokens beside a 481-token portion, 7 % / 2 % of
+        # the step faster in two launches; 32 requests of 128 to 3,200 tokens, 1.5 % slower.
+        short = list(range(head)) + list(range(tail, n))
+        enough = self.sm_count(q.device) if self.split_mixed_min_blocks is None else self.split_mixed_min_blocks
+        if self.split_mixed_attention and ctx.max_q_len > 1 and short and len(short) * nkv >= enough:
+            lens = [ctx.host["kv_lens"][e] for e in short]
+            if max(lens) * len(lens) > 1.5 * sum(lens):
+                short = []
+        else:
+            short = []
+        if not short:
+            head, tail = 0, n
+        if head > 0:
+            keys_split(0, head)
+        if tail < n:
+            keys_split(tail, n)
+        rows_entries = range(head, tail)
         def work_list(rows_per_block):
             if ctx.max_q_len == 1:
                 # decode steps (more than 16 query heads per KV head): the list depends on the number of
                 # entries alone, so it is made once and kept on the device; such steps are recorded into
                 # CUDA graphs, and a recording must not hold a copy from a buffer that lives for one step
                 lists = self.__dict__.setdefault("_decode_work_lists", {})
-                key = (q.device, ctx.n_entries, g, rows_per_block)
+                key = (q.device, ctx.n_entries, g, rows_per_block)      # (every entry: head = 0, tail = n)
                 if key not in lists:
                     tiles = (g + rows_per_block - 1) // rows_per_block
                     lists[key] = torch.tensor([(e, t) for e in range(ctx.n_entries) for t in range(tiles)],
@@ -527,8 +573,8 @@ class KernelLibrary:
             if work is None:
                 # the last row blocks of an entry see the most keys: they go first, so that the long
                 # blocks do not start when the short ones have already left the GPU half empty
-                pairs = [(e, t) for e, ql in enumerate(ctx.host["q_lens"])
-                         for t in reversed(range((ql * g + rows_per_block - 1) // rows_per_block))]
+                pairs = [(e, t) for e in rows_entries
+                         for t in reversed(range((q_lens[e] * g + rows_per_block - 1) // rows_per_block))]
                 pairs.sort(key=lambda et: -(ctx.host["starts"][et[0]] + (et[1] + 1) * rows_per_block // g))
                 work = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(q.device, non_blocking=True)
                 ctx.tables[("attention_rows_work", g, rows_per_block)] = work
@@ -538,7 +584,7 @@ class KernelLibrary:
                 and not self.force_mma_sync_prefill):
             # two row tiles per block share the key tiles and keep the tensor core busy while one of
             # them is in its softmax; one row tile per block when two would leave SMs without a block
-            pairs_of_tiles = sum((ql * g + 255) // 256 for ql in ctx.host["q_lens"]) * nkv
+            pairs_of_tiles = sum((q_lens[e] * g + 255) // 256 for e in rows_entries) * nkv
             tiles = 2 if pairs_of_tiles >= self.sm_count(q.device) else 1
             self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
                                                  work_list(128 * tiles), nq, nkv, hd, page_size, scale, window,

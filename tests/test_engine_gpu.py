@@ -158,6 +158,53 @@ def test_decode_steps_with_large_head_groups_replay_graphs(name, tmp_path_factor
     assert eng.graph_replays >= before + 20
 
 
+@pytest.mark.parametrize("which", ["B", "G", "long"])
+def test_mixed_steps_send_their_decoding_requests_to_the_keys_split_kernel(which, tmp_path_factory, long_prompt_folder):
+    """With many decoding requests of similar length beside a portion, a mixed step runs two attention
+    launches: the decoding requests at the head and at the tail of the batch on the keys-split kernel, the
+    rest on the rows-split one.  The threshold is lowered so that four requests reach it."""
+    from conftest import make_folder
+    from safetyraise_lmengine_b200.kernels import ops
+    if which == "long":
+        folder, vocab = long_prompt_folder, 512
+    else:
+        cfg, seed = TINY[which]
+        folder, vocab = make_folder(tmp_path_factory, cfg, seed, "split_" + which.lower()), cfg["vocab_size"]
+    rng = np.random.default_rng(31)
+    reqs = {r: random_tokens(rng, n, vocab) for r, n in (("a", 70), ("b", 66), ("p", 90), ("c", 72))}
+    # a, b and c are fed whole but for their last 12 tokens, which then come one by one beside portions of p;
+    # the order a, b, p, c puts decoding requests at the head and at the tail of the batch
+    steps = [{"entries": [(r, reqs[r][:-12], []) for r in ("a", "b", "c")]}]
+    for i in range(12):
+        entries = [(r, reqs[r][len(reqs[r]) - 12 + i:len(reqs[r]) - 11 + i], [0]) for r in ("a", "b")]
+        lo, hi = (0, 35) if i == 0 else (35 + 5 * (i - 1), 35 + 5 * i)
+        entries.append(("p", reqs["p"][lo:hi], list(range(hi - lo))))
+        entries.append(("c", reqs["c"][len(reqs["c"]) - 12 + i:len(reqs["c"]) - 11 + i], [0]))
+        steps.append({"entries": entries})
+    keep = ops.split_mixed_min_blocks
+    ops.split_mixed_min_blocks = 1
+    try:
+        eng = Engine_for(folder)
+        ops.begin_timing()
+        got = replay(eng, steps)
+        names = set(k.split("[")[0] for k in ops.end_timing())
+    finally:
+        ops.split_mixed_min_blocks = keep
+    assert names & {"paged_attention_decode_tma", "paged_attention_keys"}, names
+    assert names & {"paged_attention_rows", "paged_attention_rows_tma", "paged_attention_prefill_tcgen05"}, names
+    ref = {r: plain_logits(folder, t) for r, t in reqs.items()}
+    worst = 0.0
+    for (r, pos), row in got.items():
+        worst = max(worst, np.abs(row - ref[r][pos]).max() / np.abs(ref[r]).max())
+    assert len(got) == 3 * 12 + 90 and worst <= TOL["bfloat16"], worst
+
+
+def Engine_for(folder):
+    from safetyraise_lmengine_b200 import Engine
+    return Engine.from_folder(folder, dtype="bfloat16", page_size=16, num_pages=64, max_requests=4,
+                              max_batch_tokens=512, options={"cuda_graphs": False})
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_cuttings_agree_with_each_other(folder_b, dtype):
     """Beyond agreeing with the oracle: the float32 path gives the same bits however the work is cut."""
