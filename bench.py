@@ -378,7 +378,7 @@ def run_decode(args, shape: str, pk) -> dict:
     randomize_cache(eng)
     slots = fill_contexts(eng, B, context)
     with ClockSampler() as clocks:
-        d = time_decode(eng, slots, context, args.steps, args.warmup, MIN_TIMED_SECONDS)
+        d = time_decode(eng, slots, context, args.steps, args.warmup, args.min_seconds)
     ms = d["ms_per_step"]
     nbytes = decode_bytes(eng, B, d["mean_context"])
     achieved = nbytes / (ms / 1000.0) / 1e9
@@ -427,7 +427,7 @@ def run_decode(args, shape: str, pk) -> dict:
                       "tflops": round(flops / (pf_ms / 1000.0) / 1e12, 1),
                       "regime": "sustained: median of 5 runs after 3 warm-ups, back to back"}
     out["kernels"]["prefill"] = prefill_kernel_table(eng, PREFILL_TOKENS)
-    e2e, h2d, d2h, nb = time_e2e(eng, B, context, args.steps, args.warmup, ms, MIN_TIMED_SECONDS)
+    e2e, h2d, d2h, nb = time_e2e(eng, B, context, args.steps, args.warmup, ms, args.min_seconds)
     e2e_bytes = decode_bytes(eng, B, context + args.warmup + nb * args.steps // 2)
     out["e2e"] = {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                   "blocks": nb, "hbm_frac": round(e2e_bytes * e2e / B / 1e9 / pk["hbm_gbs"], 4)}
@@ -536,6 +536,8 @@ def main() -> int:
     ap.add_argument("--skip-extras", action="store_true", help="only the default decode measurement")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the block of --steps steps until this much is timed (0: one block, for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
