@@ -193,8 +193,10 @@ extern "C" int srlm_add_rmsnorm(float* residual, const void* delta, const float*
       (((uintptr_t)residual | (uintptr_t)weight) & 15) == 0 && (((uintptr_t)delta | (uintptr_t)out) & 7) == 0) {
     // whole rows in registers: one read of the residual, vector loads and stores
     const int pieces = H / 4;
+    // a thread keeps up to 4 pieces: blocks of 256 threads for rows of up to 4096 elements (several blocks
+    // share an SM and their loads overlap each other's reductions), wider blocks only for wider rows
     int block = 32;
-    while (block < 1024 && block < pieces) block <<= 1;
+    while (block < 1024 && block * 4 < pieces) block <<= 1;
     const int per_thread = (pieces + block - 1) / block;
     if (per_thread <= 1)
       launch_pdl(add_rmsnorm_vec_kernel<1>, dim3(R), dim3(block), 0, stream, residual, (const bf16*)delta, weight, eps,

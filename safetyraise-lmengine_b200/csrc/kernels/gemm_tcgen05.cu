@@ -1131,6 +1131,15 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   }
 }
 
+// The width of the token tiles this file's entry point picks for a product of M tokens and N weight
+// rows, and the tile count from which it picks 256 (for the host-side plans, which must agree with it).
+extern "C" int srlm_gemm_tcgen05_token_tile(int M, int N, int* min_tiles_for_256) {
+  if (min_tiles_for_256) *min_tiles_for_256 = BN256_MIN_TILES;
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
+  return bn;
+}
+
 // How many of the product's tiles the persistent kernel would deal out by k-blocks on the current
 // device (0: whole tiles only, or another kernel serves these sizes); for tests and notes.
 extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {

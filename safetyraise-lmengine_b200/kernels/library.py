@@ -216,14 +216,26 @@ class KernelLibrary:
             err.zero_()
         return v
 
+    # The plans below are made on the host, also where there is no GPU (tests).  They are tuned for the
+    # B200's 148 SMs, and the token-tile rule repeats the one in gemm_tcgen05.cu
+    # (srlm_gemm_tcgen05_token_tile reports the kernel's own choice; a GPU test holds the two together).
+    SMS = 148
+    BN256_MIN_TILES = 96
+
+    @staticmethod
+    def gemm_token_tile(M: int, N: int) -> int:
+        """The width of the token tiles of the tensor-core product of M tokens and N weight rows."""
+        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < KernelLibrary.BN256_MIN_TILES:
+            bn = 128                      # as the kernel's entry point chooses
+        return bn
+
     @staticmethod
     def gemm_splits(M: int, N: int, K: int) -> int:
-        """How many ways to split K: the number of blocks should fill whole waves of the 148 SMs
+        """How many ways to split K: the number of blocks should fill whole waves of the SMs
         (192 tiles alone would leave the second wave two thirds empty), each split keeping at
         least 4 k-blocks, the partial sums fitting the workspace."""
-        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < 96:
-            bn = 128                      # as the kernel's entry point chooses
+        bn = KernelLibrary.gemm_token_tile(M, N)
         if bn == 256:
             return 1                      # pairs of SMs on whole tiles of 256 x 256
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
@@ -251,7 +263,7 @@ class KernelLibrary:
             if s > 1 and (total_kb // s < 4 or 65536 + s * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES):
                 break
             blocks = tiles * s
-            eff = blocks / (-(-blocks // 148) * 148)
+            eff = blocks / (-(-blocks // KernelLibrary.SMS) * KernelLibrary.SMS)
             if eff > best_eff + 0.04:
                 best, best_eff = s, eff
         return best
@@ -443,7 +455,7 @@ class KernelLibrary:
         SM) and no more -- a few blocks left over for a second wave would double the time -- in slices of
         whole tiles."""
         tiles = max(1, (max_kv + 63) // 64)
-        nsplit = max(1, min(tiles, 296 // max(1, n_entries * nkv), max_slices))
+        nsplit = max(1, min(tiles, 2 * KernelLibrary.SMS // max(1, n_entries * nkv), max_slices))
         chunk = -(-tiles // nsplit) * 64
         nsplit = -(-tiles * 64 // chunk)
         return nsplit, chunk

@@ -8,7 +8,7 @@ the tensors it declared; it never learns which model it is in.  Five kinds:
                     rotation of q and k; ``add_to_embedding(ctx, residual)`` adds to the embedded tokens
 * Mixer:            ``cache_need()``, ``forward(ctx, x, run_step) -> [T, hidden]``
 * FeedForward:      ``forward(ctx, x) -> [T, hidden]``
-* Block:            ``forward(ctx, residual, pending, run_step) -> pending``
+* Block:            ``forward(ctx, residual, pending, run_step, next_block) -> pending`` (see ``Block``)
 
 Each kind has a registry from the ``kind`` string of its specification to the
 class; ``register_*`` adds to it, from inside or outside this package.
@@ -197,3 +197,22 @@ class Part:
 
     def cache_need(self) -> "CacheNeed":
         return type(self).cache_need_of(self.spec)
+
+
+class Block(Part):
+    """One layer: an arrangement of norms, a mixer and a feed-forward around the float32 residual stream.
+
+    ``forward(ctx, residual, pending, run_step, next_block) -> pending``.  ``residual`` [T, hidden] float32
+    is updated in place.  ``pending`` is what the block before left behind: None, a tensor still to be
+    added to the residual (the next norm kernel adds it while it norms), or a ``NormedInput`` -- the input
+    of this block's first part, already prepared by the product that wrote the residual.  A block may
+    hand its successor such a prepared input only if the successor says it takes one for this step:
+    ``next_block.prepared_input_norm(ctx)`` returns the norm whose weight the input must carry, or None
+    (the default: the successor wants a plain pending tensor).  ``next_block`` is None behind the last
+    block; what the last block returns goes to the final norm, so it must be a tensor or None."""
+
+    def prepared_input_norm(self, ctx):
+        return None
+
+    def forward(self, ctx, residual, pending, run_step, next_block=None):
+        raise NotImplementedError

@@ -11,11 +11,11 @@ from typing import List
 
 from ..config.spec import LayerSpec, RunStep
 from ..weights.loader import TensorDecl
-from .base import FEED_FORWARDS, MIXERS, NORMS, Part, lookup, register_block
+from .base import FEED_FORWARDS, MIXERS, NORMS, Block, NormedInput, lookup, register_block
 
 
 @register_block("pre_norm")
-class PreNormBlock(Part):
+class PreNormBlock(Block):
     def __init__(self, spec: LayerSpec, tensors: dict, mctx):
         p = spec.weight_prefix
         self.spec = spec
@@ -48,13 +48,17 @@ class PreNormBlock(Part):
                 and self.mixer.can_fuse(ctx) and self.feed_forward.can_fuse(ctx)
                 and not ctx.options.get("unfused_norms", False))
 
-    def forward(self, ctx, residual, pending, run_step: RunStep, next_norm=None):
-        """pending: what the block before left to be added (a tensor), or the already prepared input of
-        this block's first norm (a NormedInput), or None.  next_norm: the norm that will read the
-        residual after this block, if its block fuses too; then a NormedInput for it is returned."""
-        from .base import NormedInput
+    def prepared_input_norm(self, ctx):
+        """This block takes its input already multiplied by its first norm's weight when it fuses."""
+        return self.mixer_norm if self.fuses(ctx) else None
+
+    def forward(self, ctx, residual, pending, run_step: RunStep, next_block=None):
+        """See parts.base.Block.  When this block runs its norms inside the products around them and the
+        block behind it takes a prepared input, the down projection's epilogue prepares it."""
         T = residual.shape[0]
         if self.fuses(ctx):
+            asks = getattr(next_block, "prepared_input_norm", None)      # None behind the last block
+            next_norm = asks(ctx) if asks is not None else None
             if isinstance(pending, NormedInput):
                 nx = pending
             else:
@@ -63,7 +67,7 @@ class PreNormBlock(Part):
                 nx = NormedInput(n, None, self.hidden, self.mixer_norm.spec.eps)
             nx = self.mixer.forward_fused(ctx, nx, run_step, residual, self.ff_norm)
             return self.feed_forward.forward_fused(ctx, nx, residual, next_norm)
-        assert not isinstance(pending, NormedInput), "a fused block was promised to its predecessor"
+        assert not isinstance(pending, NormedInput), "a prepared input was handed to a block that did not ask for one"
         n = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype)
         self.mixer_norm.apply(residual, pending, n)
         mixed = self.mixer.forward(ctx, n, run_step)

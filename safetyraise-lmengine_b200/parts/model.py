@@ -101,16 +101,8 @@ class DecoderModel:
         pending = None
         order = self.spec.run_order
         for i, step in enumerate(order):
-            block = self.blocks[step.layer]
-            # a block may hand the next one its input already multiplied by that block's norm weight,
-            # if both run their norms inside the products (decode steps of a few tokens)
             nxt = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
-            next_norm = None
-            if nxt is not None and hasattr(block, "fuses") and hasattr(nxt, "fuses") and block.fuses(ctx) \
-                    and nxt.fuses(ctx):
-                next_norm = nxt.mixer_norm
-            pending = block.forward(ctx, residual, pending, step, next_norm) if hasattr(block, "fuses") \
-                else block.forward(ctx, residual, pending, step)
+            pending = self.blocks[step.layer].forward(ctx, residual, pending, step, nxt)
         # NaN and infinity stay in a residual stream that is only ever added to, and every key or value
         # a step writes is read by its own token: one look at the end covers every block
         # (src/model/native.rs:276-278, src/engine/state.rs:56-58)

@@ -394,6 +394,19 @@ def test_gemm_tcgen05_tensor_maps_survive_the_emptying_of_their_cache():
     assert ops().gemm_error_flag(torch.device(DEV)) == 0
 
 
+def test_host_plans_agree_with_the_kernels_and_the_device():
+    """The host-side plans repeat two facts of the device side: the SM count they are tuned for, and the
+    rule by which the tensor-core product picks its token tile."""
+    import ctypes as C
+    from safetyraise_lmengine_b200.kernels.library import KernelLibrary
+    assert ops().sm_count(torch.device(DEV)) == KernelLibrary.SMS
+    least = C.c_int(0)
+    for M in (1, 16, 17, 33, 64, 65, 128, 129, 256, 300, 512, 2048, 5000):
+        for N in (128, 4096, 5120, 6144, 12200, 24576, 151936):
+            assert ops().lib.srlm_gemm_tcgen05_token_tile(M, N, C.byref(least)) == KernelLibrary.gemm_token_tile(M, N), (M, N)
+    assert least.value == KernelLibrary.BN256_MIN_TILES
+
+
 def test_gemm_tcgen05_finds_each_k_and_row():
     """Identity-like operands: a misplaced row, column or k block shows as a wrong integer."""
     K, N, M = 256, 256, 40
