@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ C, int M, int N, int K,
                    long long ldx, long long ldw, long long ldc, int swiglu8, const SkinnyFuse fuse) {
   __shared__ float part[SK_WARPS][SK_ROWS][MT * 8 + 1];
-  __shared__ float row_scale[MT * 8];
+  __shared__ float ss_warp[SK_WARPS][8];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, q = lane & 3;
@@ -113,35 +113,6 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
   };
   load_w(g_lo, a[0], b[0]);
   pdl_wait();
-  if (fuse.scale_parts) {
-    // 1 / RMS of each token's row from the partial sums of squares: every thread takes one partial
-    // row (8 tokens), warps add theirs with shuffles, warp sums meet in shared memory; the order of
-    // the additions is fixed by the thread layout, and the loads fly together with the weight loads
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int p = threadIdx.x; p < fuse.n_parts; p += SK_THREADS) {
-      const float4 lo = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8));
-      const float4 hi = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8 + 4));
-      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
-      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
-    }
-#pragma unroll
-    for (int t = 0; t < 8; ++t) {
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) v[t] += __shfl_xor_sync(0xffffffffu, v[t], off);
-    }
-    if (lane == 0) {
-#pragma unroll
-      for (int t = 0; t < 8; ++t) part[warp][0][t] = v[t];      // borrowed until the epilogue fills it
-    }
-    __syncthreads();
-    if (threadIdx.x < 8) {
-      float ss = 0.f;
-#pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) ss += part[w][0][threadIdx.x];
-      row_scale[threadIdx.x] = rsqrtf(ss * fuse.inv_width + fuse.eps);
-    }
-    __syncthreads();
-  }
   // the epilogue's reads of the residual stream and of the next norm's weight are requested now, so that
   // their latency passes under the main loop instead of behind it (idx = m * 16 + row, as below)
   float res_old = 0.f, next_scale = 0.f;
@@ -182,7 +153,40 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
     part[warp][r + 8][t * 8 + 2 * q] = acc[t][2];
     part[warp][r + 8][t * 8 + 2 * q + 1] = acc[t][3];
   }
+  // 1 / RMS of each token's row from the partial sums of squares, behind the main loop: nothing in the
+  // loop needs it, and in front of it the loads and two block-wide barriers held up every warp's stream
+  // (3 us a launch, measured).  Every thread takes partial rows (8 tokens each); a warp adds its threads'
+  // rows in nine shuffles (the lanes halve the tokens they keep three times, then the four lanes of a
+  // token add up: lane 4 t ends with token t); the warps' sums meet in shared memory at the barrier the
+  // epilogue needs anyway.  The order of the additions is fixed by the thread layout.
+  if (fuse.scale_parts) {
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = threadIdx.x; p < fuse.n_parts; p += SK_THREADS) {
+      const float4 lo = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8));
+      const float4 hi = __ldg(reinterpret_cast<const float4*>(fuse.scale_parts + (size_t)p * 8 + 4));
+      v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+      v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+    }
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    float w4[4], w2[2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w4[j] = (b4 ? v[4 + j] : v[j]) + __shfl_xor_sync(0xffffffffu, b4 ? v[j] : v[4 + j], 16);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      w2[j] = (b3 ? w4[2 + j] : w4[j]) + __shfl_xor_sync(0xffffffffu, b3 ? w4[j] : w4[2 + j], 8);
+    float w1 = (b2 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? w2[0] : w2[1], 4);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+    if ((lane & 3) == 0) ss_warp[warp][lane >> 2] = w1;
+  }
   __syncthreads();
+  auto row_scale = [&](int m) {          // the warps' sums in warp order
+    float ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < SK_WARPS; ++w) ss += ss_warp[w][m & 7];
+    return rsqrtf(ss * fuse.inv_width + fuse.eps);
+  };
   if (swiglu8) {
     // the block's 16 rows are 8 gate rows then the 8 up rows of the same features: out = silu(gate) * up
     for (int idx = threadIdx.x; idx < 8 * MT * 8; idx += SK_THREADS) {
@@ -191,7 +195,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
         float gsum = 0.f, usum = 0.f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) { gsum += part[w][row][m]; usum += part[w][row + 8][m]; }
-        if (fuse.scale_parts) { gsum *= row_scale[m]; usum *= row_scale[m]; }
+        if (fuse.scale_parts) { const float sc = row_scale(m); gsum *= sc; usum *= sc; }
         const float sg = gsum >= 0.f ? gsum / (1.f + expf(-gsum)) : gsum * (expf(gsum) / (1.f + expf(gsum)));
         C[(size_t)m * ldc + (n0 >> 1) + row] = from_float<TO>(sg * usum);
       }
@@ -207,7 +211,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* _
     if (live) {
 #pragma unroll
       for (int w = 0; w < SK_WARPS; ++w) s += part[w][row][m];
-      if (fuse.scale_parts) s *= row_scale[m];
+      if (fuse.scale_parts) s *= row_scale(m);
     }
     if (!fuse.residual) {
       if (live) C[(size_t)m * ldc + n0 + row] = from_float<TO>(s);
