@@ -68,7 +68,7 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 }
 
 template <int MT, typename TO, int SK_UNROLL>     // MT token tiles of 8; SK_UNROLL groups of 32 k per batch
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, SK_UNROLL == 2 ? 3 : 1)     // the lean form: three blocks per SM
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TO* __restrict__ C, int M, int N, int K,
                    long long ldx, long long ldw, long long ldc, int swiglu8, const SkinnyFuse fuse) {
   __shared__ float part[SK_WARPS][SK_ROWS][MT * 8 + 1];
@@ -258,7 +258,24 @@ static int launch_skinny_u(const void* X, const void* W, void* C, int M, int N, 
 template <int MT, typename TO>
 static int launch_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
                          long long ldc, int swiglu8, const SkinnyFuse& fuse, int early, cudaStream_t stream) {
-  // four groups of 32 k per batch: measured best of 2 / 4 / 6 on B200 (registers against loads in flight)
+  // Four groups of 32 k per batch of loads (128 registers, two blocks per SM) stream best when the blocks
+  // fill whole rounds of two per SM.  A product of a little more than that -- up to three blocks per SM --
+  // runs as ONE round of the leaner form (two groups per batch, 80 registers, three blocks per SM)
+  // instead of a full round and a nearly empty one.  Measured on B200 (8 tokens, chains in a CUDA graph):
+  // 384 blocks (QKV at 8B sizes) 13.2 -> 10.9 us; 320 blocks (the output and down projections at 14B and 32B
+  // sizes) 14.9 -> 12.7, 44.3 -> 38.8, 23.1 -> 19.4, 64.6 -> 56.5 us; for every other block count the
+  // form with four groups is as fast or faster (256 blocks: 7.9 against 10.1 us).
+  if (MT == 1) {
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int blocks = (N + SK_ROWS - 1) / SK_ROWS;
+    if (sms > 0 && blocks > 2 * sms && blocks <= 3 * sms)
+      return launch_skinny_u<MT, TO, 2>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, early, stream);
+  }
   return launch_skinny_u<MT, TO, 4>(X, W, C, M, N, K, ldx, ldw, ldc, swiglu8, fuse, early, stream);
 }
 

@@ -644,6 +644,7 @@ def test_gemm_skinny_finds_each_k_and_row():
 
 
 @pytest.mark.parametrize("M, I, K, splits", [(1, 8, 64, 1), (8, 12288, 512, 1), (5, 24, 72, 1), (16, 256, 96, 1),
+                                             (6, 2560, 264, 1),      # 320 blocks: the lean form of the weight-streaming kernel
                                              (33, 128, 256, 2), (100, 4096, 512, 1), (64, 512, 2048, 3), (300, 200, 128, 1),
                                              (100, 512, 2048, 4), (200, 136, 1024, 2), (24, 64, 8192, 10)])
 def test_gemm_with_fused_swiglu(M, I, K, splits):
@@ -749,7 +750,8 @@ def test_paged_attention_prefill_tcgen05_refuses():
         ops().paged_attention_prefill_tcgen05(q, kc, kc, q.clone(), bt, z, z, z.view(1, 2), 2, 2, 64, 16, 1.0, 0)
 
 
-@pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 4096, 4096), (5, 200, 520), (8, 96, 264)])
+@pytest.mark.parametrize("M, N, K", [(1, 64, 64), (8, 4096, 4096), (5, 200, 520), (8, 96, 264),
+                                     (7, 5120, 1024), (8, 6144, 4096)])       # 320 and 384 blocks: the lean form
 def test_gemm_skinny_with_fused_norms(M, N, K):
     """residual += x.W^T with the next norm prepared in the epilogue, then a product that consumes it."""
     g = torch.Generator(device=DEV).manual_seed(M + N + K)
