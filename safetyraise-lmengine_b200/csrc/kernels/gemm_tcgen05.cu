@@ -1056,6 +1056,31 @@ using namespace srlm;
 
 // workspace (only when splits > 1): one int per output tile, zero on entry and left zero on exit,
 // at the start; float32 partials [splits, tiles, token tile, 128] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
+// The SM count of the current device (0 if it cannot be had).
+static int device_sms() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+// The width of a product's token tiles.  Up to 128 tokens: the smallest tile that holds them.  Beyond:
+// tiles of 256 tokens (pairs of SMs on 256 weight rows x 256 tokens) from BN256_MIN_TILES tiles of 128 rows
+// x 256 tokens on -- a pair moves half the operand bytes per SM and product of two SMs on 128 x 128 each,
+// but a narrow output has too few such tiles for every pair.  With fewer tiles, whichever form needs fewer
+// rounds of the GPU, a round of pairs (four 128 x 128 tiles' work each) counted as 4/3 rounds of single
+// SMs.  Measured at 512 tokens: 5120 x 5120 (160 tiles of 128 x 128: two rounds; 40 pairs' tiles: one)
+// 49.4 -> 33.0 us, 5120 x 8192 57.2 -> 48.1 us; 4096 x 4096 (128 tiles: one round) 22.9 us against 26.4.
+static int token_tile(int M, int N, int sms) {
+  if (M <= 128) return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  const long long rows128 = (N + BM - 1) / BM;
+  if (rows128 * ((M + 255) / 256) >= BN256_MIN_TILES) return 256;
+  if (sms <= 1) return 128;
+  const long long tiles128 = rows128 * ((M + 127) / 128), tiles256 = (long long)((N + 255) / 256) * ((M + 255) / 256);
+  const long long rounds128 = (tiles128 + sms - 1) / sms, rounds256 = (tiles256 + sms / 2 - 1) / (sms / 2);
+  return 4 * rounds256 < 3 * rounds128 ? 256 : 128;
+}
+
 extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                     long long ldx, long long ldw, long long ldc, int splits, void* workspace,
                                     long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
@@ -1074,11 +1099,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   if (splits > total_kb) splits = total_kb;
   int kb_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
-  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  // a few hundred tokens with a narrow output: token tiles of 256 would leave too many SMs without a tile
-  // (measured: worth it from two thirds of the SMs on -- a pair of SMs on 256 x 256 moves half the bytes
-  // per product of two SMs on 128 x 128 each)
-  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
+  const int bn = token_tile(M, N, device_sms());
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0, 0};
   // up to 8 splits (the portable cluster size) add their sums inside a thread-block cluster and need no
   // workspace (SRLM_GEMM_CLUSTER=0: through the workspace, as more than 8 splits do)
@@ -1135,20 +1156,15 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
 // rows, and the tile count from which it picks 256 (for the host-side plans, which must agree with it).
 extern "C" int srlm_gemm_tcgen05_token_tile(int M, int N, int* min_tiles_for_256) {
   if (min_tiles_for_256) *min_tiles_for_256 = BN256_MIN_TILES;
-  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
-  return bn;
+  return token_tile(M, N, device_sms());
 }
 
 // How many of the product's tiles the persistent kernel would deal out by k-blocks on the current
 // device (0: whole tiles only, or another kernel serves these sizes); for tests and notes.
 extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {
-  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (bn == 256 && (long long)((N + BM - 1) / BM) * ((M + 255) / 256) < BN256_MIN_TILES) bn = 128;
+  const int sm_count = device_sms();
+  const int bn = token_tile(M, N, sm_count);
   if (bn < 128) return 0;
-  int dev = 0, sm_count = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (sm_count <= 0) return 0;
   static const bool pair_off = getenv("SRLM_GEMM_PAIR") && !atoi(getenv("SRLM_GEMM_PAIR"));
   if (bn == 256 && !pair_off) return 0;       // pairs of SMs on tiles of 256 x 256: whole tiles

@@ -224,11 +224,17 @@ class KernelLibrary:
 
     @staticmethod
     def gemm_token_tile(M: int, N: int) -> int:
-        """The width of the token tiles of the tensor-core product of M tokens and N weight rows."""
-        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-        if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) < KernelLibrary.BN256_MIN_TILES:
-            bn = 128                      # as the kernel's entry point chooses
-        return bn
+        """The width of the token tiles of the tensor-core product of M tokens and N weight rows (the rule
+        of token_tile in gemm_tcgen05.cu, where its reasons and measurements stand)."""
+        if M <= 128:
+            return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+        rows128 = (N + 127) // 128
+        if rows128 * ((M + 255) // 256) >= KernelLibrary.BN256_MIN_TILES:
+            return 256
+        sms = KernelLibrary.SMS
+        tiles128, tiles256 = rows128 * ((M + 127) // 128), ((N + 255) // 256) * ((M + 255) // 256)
+        rounds128, rounds256 = -(-tiles128 // sms), -(-tiles256 // (sms // 2))
+        return 256 if 4 * rounds256 < 3 * rounds128 else 128
 
     @staticmethod
     def gemm_splits(M: int, N: int, K: int) -> int:

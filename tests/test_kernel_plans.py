@@ -27,9 +27,11 @@ def test_gemm_splits_keeps_its_bounds(M, N, K):
     assert 1 <= sp <= max(1, total_kb)
     if sp > 1:
         assert total_kb // sp >= 4                        # a split keeps at least a few k-blocks
-    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-    if bn == 256 and ((N + 127) // 128) * ((M + 255) // 256) >= 96:
+    bn = KernelLibrary.gemm_token_tile(M, N)
+    if bn == 256:
         assert sp == 1                                    # pairs of SMs on whole tiles of 256 x 256
+    assert KernelLibrary.gemm_token_tile(512, 5120) == 256 and KernelLibrary.gemm_token_tile(512, 4096) == 128
+    assert KernelLibrary.gemm_token_tile(2048, 4096) == 256 and KernelLibrary.gemm_token_tile(300, 5120) == 128
     if sp > 8:                                            # beyond a cluster: the partial sums fit the workspace
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
         assert 65536 + sp * tiles * 128 * bn * 4 <= KernelLibrary.GEMM_WS_BYTES
