@@ -17,6 +17,12 @@
 // (taken with the same reference) makes exact.  Softmax, sums and the output
 // accumulation are float32.  Every wait is bounded; when a bound is hit the block
 // raises the error flag and leaves.  Formula: src/model/math.rs:102-155.
+//
+// When the batch has too few rows for every SM (a portion of a prompt behind a long
+// context, single tokens beside it), the keys are cut into slices too: blockIdx.y
+// is the slice, a block walks only its slice's key tiles and leaves its row tiles'
+// unnormalised outputs with their reference maximum and sum in a workspace, and a
+// second kernel adds the slices of a row in slice order.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -51,6 +57,14 @@ struct Args {
   float scale_log2;
   int window;
   int* err_flag;
+  // key slices: 0 / 1 = none.  Slice z of a block is blockIdx.y and covers the keys [z, z + 1) * kv_chunk
+  // (a multiple of the key tile); then out is not written, but for the row tile `slab` = ((work item * 2 +
+  // row tile) * nkv + KV head) * nsplit + slice: part_o[slab][128 rows][128] (float32, not divided by the
+  // sum) and part_ml[slab][128 rows][2] (reference maximum in log2 units, sum; sum 0 = no key in the slice)
+  int nsplit;
+  int kv_chunk;
+  float* part_o;
+  float* part_ml;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -316,9 +330,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   const int r_last1 = min(rows_total, r_first[1] + BR) - 1;
   const int pos_first = start + r_block / g;
   const int first_key = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
-  const int jb0 = (first_key / KT) * KT;
-  const int n_tiles1 = (start + r_last1 / g + 1 - jb0 + KT - 1) / KT;
-  const int n_tiles0 = two ? (start + (r_first[1] - 1) / g + 1 - jb0 + KT - 1) / KT : 0;
+  const int jb_window = (first_key / KT) * KT;
+  const bool sliced = a.nsplit > 1;
+  const int slice_lo = sliced ? (int)blockIdx.y * a.kv_chunk : 0;
+  const int slice_hi = sliced ? slice_lo + a.kv_chunk : 0x7fffffff - KT;
+  const int jb0 = max(jb_window, slice_lo);
+  // the keys a row tile sees end behind its last row's position; a slice ends them earlier
+  const int end1 = min(start + r_last1 / g + 1, slice_hi);
+  const int end0 = two ? min(start + (r_first[1] - 1) / g + 1, slice_hi) : 0;
+  const int n_tiles1 = end1 > jb0 ? (end1 - jb0 + KT - 1) / KT : 0;
+  const int n_tiles0 = end0 > jb0 ? (end0 - jb0 + KT - 1) / KT : 0;
   // V tiles that hold rows without a key of this request (beyond its length, before the window)
   const bool dirty_first = a.window > 0 && jb0 < first_key;
   const bool dirty_last = jb0 + n_tiles1 * KT > kv_len;
@@ -360,7 +381,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
         tma_load_2d(tile + KT * 128 + lane * box_rows * 128, map, full, 64, row);
       }
     };
-    bool ok = true;
+    bool ok = n_tiles1 > 0;             // a slice beyond the block's last key has nothing to fetch
     auto load_v = [&](int tv) {
       const int sv = tv % KV_STAGES;
       ok = mbar_wait(&v_empty[sv], ((tv / KV_STAGES) & 1) ^ 1, a.err_flag, 47);
@@ -395,7 +416,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    if (lane == 0 && n_tiles1 > 0) {
       const uint32_t idesc_s = umma_idesc(KT, false), idesc_o = umma_idesc(HD, true);
       bool ok = true;
       auto wait_k = [&](int t) {
@@ -510,10 +531,29 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[i]);
     }
-    // the output row: O / l
     if (ok && n_tiles > 0) ok = mbar_wait(&o_done[i], (n_tiles - 1) & 1, a.err_flag, 46);
     fence_after();
-    if (n_tiles > 0 && __all_sync(0xffffffffu, ok)) {      // the loads are warp-wide: rows beyond the tile run them too
+    const bool have = n_tiles > 0 && __all_sync(0xffffffffu, ok);   // the loads are warp-wide: rows beyond the tile run them too
+    if (sliced) {
+      // this slice's share of the row: unnormalised, with the reference of its exponentials and its sum
+      if (i == 1 || two) {
+        const size_t slab = (((size_t)item * 2 + i) * a.nkv + kvh) * a.nsplit + blockIdx.y;
+        *reinterpret_cast<float2*>(a.part_ml + (slab * BR + row) * 2) = make_float2(m_run, have ? l_run : 0.f);
+        if (have) {
+          float* dst = a.part_o + (slab * BR + row) * HD;
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(o_addr + c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(dst + c + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+        }
+      }
+    } else if (have) {
+      // the output row: O / l
       const bool mine = r < min(r_first[i] + BR, r_end);
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int rr = min(r, r_end - 1);
@@ -541,6 +581,56 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// Adds the key slices of every row tile: blockIdx.x = (work item, row tile, KV head), blockIdx.y = eight of
+// the tile's rows, a warp takes one row, a lane four of its 128 dimensions.  out = sum_z O_z 2^(m_z - M) / sum_z l_z 2^(m_z - M) with M
+// the largest reference among the slices that saw a key; slices are added in slice order.
+__global__ void __launch_bounds__(256) attention_prefill_merge_kernel(const Args a) {
+  pdl_wait();
+  pdl_trigger();
+  const int kvh = blockIdx.x % a.nkv, i = (blockIdx.x / a.nkv) & 1, item = blockIdx.x / (2 * a.nkv);
+  const int e = a.work[2 * item], bt = a.work[2 * item + 1];
+  const int g = a.nq / a.nkv;
+  const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0;
+  const int rows_total = q_len * g;
+  const int r_block = bt * a.tiles_per_block * BR;
+  const bool two = a.tiles_per_block == 2 && r_block + BR < rows_total;
+  if (i == 0 && !two) return;
+  const int r_first = i ? (two ? r_block + BR : r_block) : r_block;
+  const int r_end = i ? rows_total : r_block + BR;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t slab0 = (((size_t)item * 2 + i) * a.nkv + kvh) * a.nsplit;
+  const int row = blockIdx.y * 8 + warp;
+  if (r_first + row < r_end) {
+    float m_z = -CUDART_INF_F, l_z = 0.f;
+    if (lane < a.nsplit) {
+      const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + ((slab0 + lane) * BR + row) * 2);
+      m_z = ml.y > 0.f ? ml.x : -CUDART_INF_F;
+      l_z = ml.y;
+    }
+    float M = m_z;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    const float w_z = l_z > 0.f ? exp2f(m_z - M) : 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+    for (int z = 0; z < a.nsplit; ++z) {
+      const float w = __shfl_sync(0xffffffffu, w_z, z);
+      L += w * __shfl_sync(0xffffffffu, l_z, z);
+      if (w > 0.f) {
+        const float4 o = *reinterpret_cast<const float4*>(a.part_o + ((slab0 + z) * BR + row) * HD + lane * 4);
+        acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+      }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int rr = r_first + row;
+    bf16* dst = a.out + ((size_t)(q0 + rr / g) * a.nq + kvh * g + rr % g) * HD + lane * 4;
+    uint2 o2;
+    o2.x = pack2(acc.x * inv, acc.y * inv);
+    o2.y = pack2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(dst) = o2;
   }
 }
 
@@ -602,13 +692,20 @@ extern "C" int srlm_attention_prefill_tcgen05_takes(int hd, int page_size) {
 }
 
 // Ragged batch; work: n_work pairs (entry, block of tiles_per_block x 128 rows), rows = query tokens x
-// (nq / nkv); tiles_per_block is 1 or 2.
+// (nq / nkv); tiles_per_block is 1 or 2.  nsplit > 1 cuts the keys into slices of kv_chunk (a multiple of
+// 128) with a block each; part_o then holds n_work * 2 * nkv * nsplit * 128 * 128 floats and part_ml
+// n_work * 2 * nkv * nsplit * 128 * 2, and a second kernel adds the slices.
 extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
                                                     long long num_pages, const int* block_table, int table_stride,
                                                     const int* cu_q, const int* kv_lens, const int* work, int n_work,
                                                     int nq, int nkv, int hd, int page_size, float scale, int window,
-                                                    int tiles_per_block, int* err_flag, cudaStream_t stream) {
+                                                    int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
+                                                    float* part_ml, int* err_flag, cudaStream_t stream) {
   if (n_work <= 0) return ST_OK;
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > 1 && (nsplit > 32 || kv_chunk <= 0 || kv_chunk % fmha::KT || !part_o || !part_ml))
+    return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: nsplit=%d kv_chunk=%d (slices of whole key tiles, at most 32, "
+                  "with their workspace)", nsplit, kv_chunk);
   if (!srlm_attention_prefill_tcgen05_takes(hd, page_size) || nq <= 0 || nkv <= 0 || nq % nkv ||
       tiles_per_block < 1 || tiles_per_block > 2)
     return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: nq=%d nkv=%d hd=%d page_size=%d tiles_per_block=%d", nq,
@@ -628,8 +725,11 @@ extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k
     configured = true;
   }
   fmha::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, page_size,
-               tiles_per_block, scale * 1.4426950408889634f, window, err_flag};
-  launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work * nkv), dim3(fmha::THREADS), SMEM, stream, *mk, *mv, a);
+               tiles_per_block, scale * 1.4426950408889634f, window, err_flag, nsplit, kv_chunk, part_o, part_ml};
+  launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work * nkv, nsplit), dim3(fmha::THREADS), SMEM, stream,
+             *mk, *mv, a);
+  if (nsplit > 1)
+    launch_pdl(fmha::attention_prefill_merge_kernel, dim3(n_work * 2 * nkv, fmha::BR / 8), dim3(256), 0, stream, a);
   return launched();
 }
 

@@ -54,6 +54,7 @@ class KernelLibrary:
         self.fuse_decode_attention = True       # decode: norm, rotation and append inside the attention kernel
         self.force_mma_sync_prefill = False
         self.split_mixed_attention = True       # mixed steps: decoding requests to the keys-split kernel ...
+        self.split_prefill_keys = True          # rows-split attention: the keys in slices when rows are few
         self.split_mixed_min_blocks = None      # ... when they make this many blocks (None: one per SM)
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
 
@@ -388,16 +389,50 @@ class KernelLibrary:
             _ptr(err), _stream()), "paged_attention_rows_tma")
 
     def paged_attention_prefill_tcgen05(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv,
-                                        hd, page_size, scale, window=0, tiles_per_block=2):
+                                        hd, page_size, scale, window=0, tiles_per_block=2, nsplit=1, kv_chunk=0,
+                                        part_o=None, part_ml=None):
         """Rows-split attention on tcgen05 tensor cores with accumulators in tensor memory (head size
         128; page_size 8..64 a power of two, or a multiple of 128); work: int32 [n, 2] (entry, block of
-        tiles_per_block x 128 rows), tiles_per_block 1 or 2."""
+        tiles_per_block x 128 rows), tiles_per_block 1 or 2.  nsplit > 1: the keys in slices of kv_chunk
+        (a multiple of 128), a block each, added by a second kernel; part_o float32
+        [n * 2 * nkv * nsplit * 128, 128] and part_ml [.., 2] are their workspace."""
         err = self._gemm_state(q.device)[1]
         self._check(self.lib.srlm_paged_attention_prefill_tcgen05(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
             C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
             C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
-            C.c_int(tiles_per_block), _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
+            C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(err),
+            _stream()), "paged_attention_prefill_tcgen05")
+        if nsplit > 1:
+            self.launches += 1           # the kernel that adds the slices
+
+    @staticmethod
+    def prefill_attention_plan(rows, kv_lens, nkv: int, sms: int):
+        """(tiles_per_block, nsplit, kv_chunk) for the tensor-memory attention kernel on entries of
+        ``rows`` rows (tokens x query heads per KV head) and ``kv_lens`` keys.  The choice goes by a
+        model of the kernel's time, fitted to measurements on B200 (one portion of 481 to 512 tokens behind
+        1,024 and 8,192 cached ones, 32 and 40 heads over 8 KV heads), in microseconds: a block of one row
+        tile takes 7.8 + 1.75 a key tile, a block of two row tiles 11.7 + 1.92 a key tile (the tensor core
+        works on one tile while the other is in its softmax), blocks run in rounds of one per SM, and
+        cutting the keys into slices adds 11 (the slices' outputs go through a workspace and a second
+        kernel).  So: two row tiles a block when the rows fill the SMs or one-tile blocks would need a
+        round more; key slices for a portion behind a long context (512 tokens behind 8,192: 126.6 us in
+        one-tile blocks, 88.6 us in two slices of two-tile blocks)."""
+        two_tile_blocks = sum((r + 255) // 256 for r in rows) * nkv
+        one_tile_blocks = sum((r + 127) // 128 for r in rows) * nkv
+        key_tiles = max(1, (max(kv_lens) + 127) // 128)
+        rounds = lambda blocks: -(-blocks // max(1, sms))
+        best = (rounds(one_tile_blocks) * (key_tiles * 1.75 + 7.8), 1, 1)
+        for s in range(1, min(16, max(1, key_tiles // 2)) + 1):
+            per_slice = -(-key_tiles // s)
+            t = rounds(two_tile_blocks * s) * (per_slice * 1.92 + 11.7) + (11.0 if s > 1 else 0.0)
+            if t < best[0] - 1e-9:
+                best = (t, 2, s)
+        _, tiles, s = best
+        if s == 1:
+            return tiles, 1, 0
+        chunk = -(-key_tiles // s) * 128
+        return tiles, -(-key_tiles * 128 // chunk), chunk
 
     def paged_attention_keys(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, n_entries, nq, nkv, hd,
                              page_size, scale, window, kv_chunk, nsplit, part_o=None, part_ml=None):
@@ -600,13 +635,22 @@ class KernelLibrary:
 
         if (self.lib.srlm_attention_prefill_tcgen05_takes(C.c_int(hd), C.c_int(page_size))
                 and not self.force_mma_sync_prefill):
-            # two row tiles per block share the key tiles and keep the tensor core busy while one of
-            # them is in its softmax; one row tile per block when two would leave SMs without a block
-            pairs_of_tiles = sum((q_lens[e] * g + 255) // 256 for e in rows_entries) * nkv
-            tiles = 2 if pairs_of_tiles >= self.sm_count(q.device) else 1
-            self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens,
-                                                 work_list(128 * tiles), nq, nkv, hd, page_size, scale, window,
-                                                 tiles)
+            rows = [q_lens[e] * g for e in rows_entries]
+            # a decode step may be replayed from a CUDA graph with longer contexts than it was recorded
+            # with: its plan goes by the bound that is part of the graph's identity
+            lens = [ctx.kv_bound] if ctx.max_q_len == 1 else [ctx.host["kv_lens"][e] for e in rows_entries]
+            tiles, nsplit, chunk = self.prefill_attention_plan(rows, lens, nkv, self.sm_count(q.device))
+            if not self.split_prefill_keys:
+                nsplit, chunk = 1, 0
+            work = work_list(128 * tiles)
+            part_o = part_ml = None
+            if nsplit > 1:
+                slabs = work.shape[0] * 2 * nkv * nsplit * 128
+                part_o = ctx.workspace.get("attn.rows_part_o", slabs, hd, torch.float32, reserve=0)
+                part_ml = ctx.workspace.get("attn.rows_part_ml", slabs, 2, torch.float32, reserve=0)
+            self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work,
+                                                 nq, nkv, hd, page_size, scale, window, tiles, nsplit, chunk, part_o,
+                                                 part_ml)
             return
         tma = (hd in (64, 128) and self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))
                and not self.force_cp_async_decode)

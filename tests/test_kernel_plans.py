@@ -35,3 +35,21 @@ def test_gemm_splits_keeps_its_bounds(M, N, K):
     if sp > 8:                                            # beyond a cluster: the partial sums fit the workspace
         tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
         assert 65536 + sp * tiles * 128 * bn * 4 <= KernelLibrary.GEMM_WS_BYTES
+
+
+def test_prefill_attention_plan():
+    plan = KernelLibrary.prefill_attention_plan
+    # a whole prompt of 2,048 tokens, 4 heads per KV head, 8 KV heads: enough blocks of two row tiles, no slices
+    assert plan([8192], [2048], 8, 148) == (2, 1, 0)
+    # a portion of 512 tokens behind 30,000: 64 blocks of two row tiles; the keys go in slices of whole tiles
+    tiles, nsplit, chunk = plan([2048], [30512], 8, 148)
+    assert tiles == 2 and nsplit >= 2 and chunk % 128 == 0 and nsplit * chunk >= 30512 > (nsplit - 1) * chunk
+    # 152 lone row tiles would need two rounds of the GPU, 80 blocks of two tiles one: two tiles, no slices
+    assert plan([2405], [1505], 8, 148) == (2, 1, 0)
+    # a handful of rows and keys: nothing to cut
+    assert plan([5], [100], 1, 148)[1:] == (1, 0)
+    for rows, kv, nkv in (([1, 4000], [9000, 4000], 2), ([300] * 40, [5000] * 40, 8), ([128], [257], 1)):
+        tiles, nsplit, chunk = plan(rows, kv, nkv, 148)
+        assert tiles in (1, 2) and 1 <= nsplit <= 16
+        if nsplit > 1:
+            assert tiles == 2 and chunk % 128 == 0 and nsplit * chunk >= max(kv) > (nsplit - 1) * chunk - 128

@@ -706,6 +706,19 @@ def test_paged_attention_rows_tma(nq, nkv, hd, ps, window):
 def test_paged_attention_prefill_tcgen05(nq, nkv, ps, window, tiles):
     """The tcgen05 prefill attention: ragged entries, partly filled pages, pages of other requests and
     unwritten page tails poisoned with NaN, a far key that must win the softmax."""
+    check_prefill_tcgen05(nq, nkv, ps, window, tiles, 1, 0)
+
+
+@pytest.mark.parametrize("nq, nkv, ps", [(32, 8, 16), (4, 4, 32), (6, 2, 128)])
+@pytest.mark.parametrize("window", [0, 37, 200])
+@pytest.mark.parametrize("tiles, nsplit, chunk", [(2, 3, 256), (1, 2, 384), (2, 6, 128)])
+def test_paged_attention_prefill_tcgen05_key_slices(nq, nkv, ps, window, tiles, nsplit, chunk):
+    """The same with the keys cut into slices: slices beyond an entry's keys, slices that end inside a
+    row tile's diagonal, a window that starts inside a later slice; the workspace starts as NaN."""
+    check_prefill_tcgen05(nq, nkv, ps, window, tiles, nsplit, chunk)
+
+
+def check_prefill_tcgen05(nq, nkv, ps, window, tiles, nsplit, chunk):
     hd = 128
     lens_q, lens_kv = [1, 7, 33, 1, 2, 150, 300, 520], [1, 40, 33, 65, 100, 300, 300, 700]
     pages = 120 + sum(-(-kv // ps) for kv in lens_kv)
@@ -733,7 +746,13 @@ def test_paged_attention_prefill_tcgen05(nq, nkv, ps, window, tiles):
                         dtype=torch.int32, device=DEV)
     out = torch.full_like(q, float("nan"))
     scale = 1 / math.sqrt(hd)
-    ops().paged_attention_prefill_tcgen05(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, scale, window, tiles)
+    part_o = part_ml = None
+    if nsplit > 1:
+        slabs = work.shape[0] * 2 * nkv * nsplit * 128
+        part_o = torch.full((slabs, hd), float("nan"), device=DEV)
+        part_ml = torch.full((slabs, 2), float("nan"), device=DEV)
+    ops().paged_attention_prefill_tcgen05(q, kc, vc, out, bt, cu, kvl, work, nq, nkv, hd, ps, scale, window, tiles,
+                                          nsplit, chunk, part_o, part_ml)
     torch.cuda.synchronize()
     assert ops().gemm_error_flag(q.device) == 0
     kc, vc = torch.nan_to_num(kc), torch.nan_to_num(vc)
