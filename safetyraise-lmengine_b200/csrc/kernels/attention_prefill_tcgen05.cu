@@ -347,16 +347,32 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
   if (warp != 0) {
     // Q rows -> shared memory in the swizzled K-major layout (zeros beyond the entry's rows), while
     // warp 0 already fetches the first keys
-    for (int idx = threadIdx.x - 32; idx < (two ? 2 : 1) * BR * 16; idx += THREADS - 32) {
-      const int row = idx >> 4, c = idx & 15;
-      const int r = r_block + row;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < rows_total)
-        v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + r / g) * a.nq + kvh * g + r % g) * HD + c * 8);
-      // a block of one row tile keeps it in slot 1
-      const uint32_t tile = s32(q_t) + ((two ? row >> 7 : 1) * TILE_BYTES);
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr(tile, row & 127, c)), "r"(v.x), "r"(v.y),
-                   "r"(v.z), "r"(v.w) : "memory");
+    // (eight loads in flight per thread, then their stores: a store after every load would make each
+    // load wait for the one before it, fourteen round trips to memory in a row)
+    constexpr int QB = 8;
+    const int total = (two ? 2 : 1) * BR * 16;
+    for (int base = threadIdx.x - 32; base < total; base += (THREADS - 32) * QB) {
+      uint4 v[QB];
+#pragma unroll
+      for (int j = 0; j < QB; ++j) {
+        const int idx = base + j * (THREADS - 32);
+        const int row = idx >> 4, c = idx & 15;
+        const int r = r_block + row;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (idx < total && r < rows_total)
+          v[j] = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)(q0 + r / g) * a.nq + kvh * g + r % g) * HD + c * 8));
+      }
+#pragma unroll
+      for (int j = 0; j < QB; ++j) {
+        const int idx = base + j * (THREADS - 32);
+        if (idx < total) {
+          const int row = idx >> 4, c = idx & 15;
+          // a block of one row tile keeps it in slot 1
+          const uint32_t tile = s32(q_t) + ((two ? row >> 7 : 1) * TILE_BYTES);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile_addr(tile, row & 127, c)), "r"(v[j].x),
+                       "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
+        }
+      }
     }
     fence_async_smem();
     __syncwarp();
