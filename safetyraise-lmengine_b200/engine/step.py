@@ -58,9 +58,10 @@ class PreparedStep:
     token_at: List[int]               # offset of each entry's first token id in the buffer
     missing: int                      # token ids still to be set
     state_snapshot: Optional[dict] = None   # fixed-size state of the step's slots before the forward
+    host: Optional[np.ndarray] = None       # the pinned buffer as an array (made once: set_token is called per token)
 
     def set_token(self, entry: int, index: int, token: int) -> None:
-        h = self.pair[0].numpy()
+        h = self.host if self.host is not None else self.pair[0].numpy()
         at = self.token_at[entry] + index
         if h[at] == LATER:
             self.missing -= 1
@@ -269,7 +270,7 @@ class Engine:
         view("slots")[:] = [e.slot for e in entries]
         view("kv_lens")[:] = kv_lens
         return PreparedStep(entries=entries, starts=starts, q_lens=q_lens, kv_lens=kv_lens, sections=sections,
-                            words=off, pair=pair, pages=pages, wanted=R, token_at=token_at, missing=missing)
+                            words=off, pair=pair, pages=pages, wanted=R, token_at=token_at, missing=missing, host=h)
 
     def _upload(self, prep: PreparedStep) -> StepContext:
         """Copies the laid-out batch to the device in one copy and returns the device views."""
