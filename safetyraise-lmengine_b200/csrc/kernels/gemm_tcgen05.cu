@@ -168,6 +168,27 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
+// Optional fusions of the one-tile kernel with the norms around a product (decode steps of 9 to 64 tokens;
+// the same scheme as the weight-streaming kernel's, gemm_skinny.cu):
+//  * scale_parts [n_parts][ld_parts]: the tokens X are (residual * norm weight) in bfloat16, not yet divided
+//    by their RMS; the product is scaled per token by rsqrt(sum_p scale_parts[p][token] / norm_width + eps).
+//  * residual [M][ldr] float32: the product is added to it in place instead of being stored; with next_w [N]
+//    also xw_out [M][ldxw] = bf16(residual * next_w) and ss_out [N tiles][ld_ss] (each tile's share of the
+//    rows' sums of squares) are written for the norm that follows.
+struct GemmFuse {
+  const float* scale_parts;
+  int n_parts;
+  long long ld_parts;
+  float inv_width, eps;
+  float* residual;
+  long long ldr;
+  const float* next_w;
+  bf16* xw_out;
+  long long ldxw;
+  float* ss_out;
+  long long ld_ss;
+};
+
 struct GemmArgs {
   void* C;
   int c_is_f32;
@@ -183,6 +204,7 @@ struct GemmArgs {
                            //    through distributed shared memory; partial and tile_counters are not used
   int sk_tiles, sk_blocks; // persistent kernel: the k-blocks of the first sk_tiles tiles are dealt out evenly to
                            //    the first sk_blocks blocks (0: every block takes whole tiles only)
+  GemmFuse fuse;           // one-tile kernel only; all zero: none
 };
 
 __device__ __forceinline__ void cluster_sync_all() {   // every thread of every block of the cluster
@@ -245,6 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  float* ss_half = reinterpret_cast<float*>(tmem_slot + 4);     // [2][64]: halves of the tokens' sums of squares
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -278,7 +301,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int ew = warp & 3;
   const int rows = min(BN, args.M - m0);
   bool finish = false;
-  int m_first = ew, m_step = 4;
+  const bool split = gridDim.z > 1 && !args.clustered;
+  // which tokens this thread finishes: every 4th of the tile, or, of a cluster's tile, every 4th of block z's
+  const int m_first = args.clustered ? (int)blockIdx.z + (int)gridDim.z * ew : ew;
+  const int m_step = args.clustered ? 4 * (int)gridDim.z : 4;
+
+  // What the fused final stage reads from global memory besides the accumulator: the partial sums of squares
+  // of the tile's tokens, this thread's rows of the residual stream and the next norm's weights.  The epilogue
+  // warps request the first of it before they wait for the accumulator, so that it arrives under the main loop.
+  const GemmFuse& f = args.fuse;
+  constexpr int GROUP = 4;                 // tokens of a thread whose residual rows are in flight together
+  float4 held[GROUP], next_w4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int col_f = n0 + 4 * lane;
+  const bool res_vec = col_f + 4 <= args.N && f.ldr % 4 == 0 && (reinterpret_cast<uintptr_t>(f.residual) & 15) == 0;
+  auto residual_rows = [&](float4 (&into)[GROUP], const int m_from) {
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      const int m = m_from + j * m_step;
+      float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < rows) {
+        const float* res = f.residual + (size_t)(m0 + m) * f.ldr + col_f;
+        if (res_vec) {
+          r = *reinterpret_cast<const float4*>(res);
+        } else {
+          if (col_f < args.N) r.x = res[0];
+          if (col_f + 1 < args.N) r.y = res[1];
+          if (col_f + 2 < args.N) r.z = res[2];
+          if (col_f + 3 < args.N) r.w = res[3];
+        }
+      }
+      into[j] = r;
+    }
+  };
+  const bool fused = BN <= 64 && (f.scale_parts != nullptr || f.residual != nullptr);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -333,11 +388,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // the lanes of a warp side by side: thread (warp ew, lane) then owns the tokens ew, ew + 4, ...
     // and the four weight rows 4 * lane .. 4 * lane + 3 of each.
     pdl_wait();
+    if (fused) {
+      if (f.scale_parts) {
+        // thread t adds every second part of token t % 64 (neighbouring threads, neighbouring tokens); the two
+        // halves meet in shared memory behind the barrier below
+        const int t = threadIdx.x - 64, m = t & 63;
+        float p = 0.f;
+        if (m < rows)
+          for (int q = t >> 6; q < f.n_parts; q += 2) p += __ldg(f.scale_parts + (size_t)q * f.ld_parts + m0 + m);
+        ss_half[t] = p;
+      }
+      if (f.residual && !split) residual_rows(held, m_first);   // (splits in global memory: the owner is not known yet)
+      if (f.next_w) {
+        if (col_f < args.N) next_w4.x = __ldg(f.next_w + col_f);
+        if (col_f + 1 < args.N) next_w4.y = __ldg(f.next_w + col_f + 1);
+        if (col_f + 2 < args.N) next_w4.z = __ldg(f.next_w + col_f + 2);
+        if (col_f + 3 < args.N) next_w4.w = __ldg(f.next_w + col_f + 3);
+      }
+    }
     const bool ok = mbar_wait(accum_bar, 0, args.err_flag, 3);
     tcgen05_fence_after();
     const int lane_base = 32 * ew;                      // the TMEM lanes this warp may read
     constexpr int CH = BN < 32 ? 16 : 32;
-    const bool split = gridDim.z > 1 && !args.clustered;
     if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
@@ -405,9 +477,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // block passes both cluster barriers: no path above leaves the kernel.
     cluster_sync_all();
     if (warp >= 2) {
-      const int nz = (int)gridDim.z, z = (int)blockIdx.z;
-      m_first = z + nz * ew;
-      m_step = 4 * nz;
+      const int nz = (int)gridDim.z;
       for (int m = m_first; m < rows; m += 2 * m_step) {
         const int m2 = m + m_step < rows ? m + m_step : m;       // two rows at a time: 2 nz loads in flight
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
@@ -423,7 +493,100 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       __syncwarp();                          // SwiGLU reads the up rows from another lane's columns
     }
   }
-  if (warp >= 2) {
+  if (warp >= 2 && finish && fused) {
+    // ---- rows of the slab -> C or the residual stream, with the norms around the product folded in ----
+    // 1 / RMS of token m: the halves are added in one order
+    auto scale_of = [&](const int m) {
+      return f.scale_parts ? rsqrtf((ss_half[m] + ss_half[64 + m]) * f.inv_width + f.eps) : 1.f;
+    };
+    const int esize = args.c_is_f32 ? 4 : 2;
+    const bool vec_ok = (args.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
+    auto store4 = [&](uint8_t* dst, const float (&h)[4], const bool whole, const int left) {
+      if (vec_ok && whole) {
+        if (args.c_is_f32) {
+          *reinterpret_cast<float4*>(dst) = make_float4(h[0], h[1], h[2], h[3]);
+        } else {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(h[0], h[1]), hi = __floats2bfloat162_rn(h[2], h[3]);
+          uint2 pk;
+          pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(dst) = pk;
+        }
+      } else {
+        for (int e = 0; e < 4 && e < left; ++e) {
+          if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = h[e];
+          else reinterpret_cast<bf16*>(dst)[e] = __float2bfloat16_rn(h[e]);
+        }
+      }
+    };
+    auto one_token = [&](const int m, const float sc, const float4 r) {
+      if (args.swiglu8) {
+        if ((lane & 3) < 2) {
+          const int col = (n0 >> 1) + (lane >> 2) * 8 + (lane & 1) * 4;
+          const int width = args.N >> 1;
+          const float4 g = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
+          const float4 u = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane + 8);
+          const float h[4] = {silu_stable(g.x * sc) * (u.x * sc), silu_stable(g.y * sc) * (u.y * sc),
+                              silu_stable(g.z * sc) * (u.z * sc), silu_stable(g.w * sc) * (u.w * sc)};
+          store4(reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + m) * args.ldc + col) * esize, h,
+                 col + 4 <= width, width - col);
+        }
+        return;
+      }
+      const int col = col_f;
+      const float4 x4 = *reinterpret_cast<const float4*>(slab + m * SROW + 4 * lane);
+      float h[4] = {x4.x * sc, x4.y * sc, x4.z * sc, x4.w * sc};
+      if (!f.residual) {
+        store4(reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + m) * args.ldc + col) * esize, h,
+               col + 4 <= args.N, args.N - col);
+        return;
+      }
+      // residual += product; the next norm's input and this tile's share of the row's sum of squares
+      float* res = f.residual + (size_t)(m0 + m) * f.ldr + col;
+      h[0] += r.x; h[1] += r.y; h[2] += r.z; h[3] += r.w;
+      if (res_vec) {
+        *reinterpret_cast<float4*>(res) = make_float4(h[0], h[1], h[2], h[3]);
+      } else {
+        for (int e = 0; e < 4; ++e) {
+          if (col + e < args.N) res[e] = h[e]; else h[e] = 0.f;
+        }
+      }
+      if (f.next_w) {
+        const float y[4] = {h[0] * next_w4.x, h[1] * next_w4.y, h[2] * next_w4.z, h[3] * next_w4.w};
+        bf16* xw = f.xw_out + (size_t)(m0 + m) * f.ldxw + col;
+        if (col + 4 <= args.N && f.ldxw % 4 == 0 && (reinterpret_cast<uintptr_t>(f.xw_out) & 7) == 0) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+          uint2 pk;
+          pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(xw) = pk;
+        } else {
+          for (int e = 0; e < 4 && col + e < args.N; ++e) xw[e] = __float2bfloat16_rn(y[e]);
+        }
+        float sq = h[0] * h[0] + h[1] * h[1] + h[2] * h[2] + h[3] * h[3];      // (columns past N hold 0)
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        if (lane == 0) f.ss_out[(size_t)blockIdx.x * f.ld_ss + m0 + m] = sq;
+      }
+    };
+    if (!f.residual) {
+#pragma unroll 1
+      for (int m = m_first; m < rows; m += m_step) one_token(m, scale_of(m), next_w4);
+    } else {
+      // four tokens at a time; the rows of the next four are requested before these are worked on
+      if (split) residual_rows(held, m_first);
+#pragma unroll 1
+      for (int m = m_first; m < rows; m += GROUP * m_step) {
+        float4 ahead[GROUP];
+        if (m + GROUP * m_step < rows) residual_rows(ahead, m + GROUP * m_step);
+#pragma unroll
+        for (int j = 0; j < GROUP; ++j)
+          if (m + j * m_step < rows) one_token(m + j * m_step, scale_of(m + j * m_step), held[j]);
+#pragma unroll
+        for (int j = 0; j < GROUP; ++j) held[j] = ahead[j];
+      }
+    }
+  } else if (warp >= 2) {
     if (finish) {
       // rows of the slab -> C
       const int esize = args.c_is_f32 ? 4 : 2;
@@ -931,7 +1094,7 @@ extern "C" int srlm_gemm_tcgen05_map_cache(int* limit) {
 
 template <int BN, int STAGES>
 static int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, int splits, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * stage_bytes<BN>() + (2 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr int SMEM = STAGES * stage_bytes<BN>() + (2 * STAGES + 1) * 8 + 16 + 512 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
@@ -1081,9 +1244,9 @@ static int token_tile(int M, int N, int sms) {
   return 4 * rounds256 < 3 * rounds128 ? 256 : 128;
 }
 
-extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
-                                    long long ldx, long long ldw, long long ldc, int splits, void* workspace,
-                                    long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
+static int gemm_entry(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K, long long ldx,
+                      long long ldw, long long ldc, int splits, void* workspace, long long workspace_bytes,
+                      int* err_flag, int swiglu8, const GemmFuse* fuse, cudaStream_t stream) {
   if (M <= 0) return ST_OK;
   if (N <= 0 || K <= 0 || ldx < K || ldw < K || ldc < (swiglu8 ? N / 2 : N) || (swiglu8 && N % 16))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05: M=%d N=%d K=%d ldx=%lld ldw=%lld ldc=%lld swiglu8=%d", M, N, K, ldx,
@@ -1101,6 +1264,11 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
   splits = (total_kb + kb_per_split - 1) / kb_per_split;       // no empty split
   const int bn = token_tile(M, N, device_sms());
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0, 0};
+  if (fuse) {
+    if (bn > 64)
+      return refuse(ST_BAD_SIZE, "gemm_tcgen05: the norm fusions take at most 64 tokens, got %d", M);
+    a.fuse = *fuse;
+  }
   // up to 8 splits (the portable cluster size) add their sums inside a thread-block cluster and need no
   // workspace (SRLM_GEMM_CLUSTER=0: through the workspace, as more than 8 splits do)
   static const bool cluster_off = getenv("SRLM_GEMM_CLUSTER") && !atoi(getenv("SRLM_GEMM_CLUSTER"));
@@ -1150,6 +1318,40 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
     case 128: return launch<128, 3>(mw, mx, a, splits, stream);
     default: return launch<256, 4>(mw, mx, a, splits, stream);
   }
+}
+
+extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                    long long ldx, long long ldw, long long ldc, int splits, void* workspace,
+                                    long long workspace_bytes, int* err_flag, int swiglu8, cudaStream_t stream) {
+  return gemm_entry(X, W, C, c_dtype, M, N, K, ldx, ldw, ldc, splits, workspace, workspace_bytes, err_flag, swiglu8,
+                    nullptr, stream);
+}
+
+// The same product for 9 to 64 tokens fused with the norms around it (see GemmFuse).  scale_parts may be
+// null (X is already normalised); residual may be null (the product is stored to C, possibly through
+// SwiGLU); with residual C is not written and may be null.
+extern "C" int srlm_gemm_tn_tcgen05_fused(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                          long long ldx, long long ldw, long long ldc, int splits, void* workspace,
+                                          long long workspace_bytes, int* err_flag, int swiglu8,
+                                          const float* scale_parts, int n_parts, long long ld_parts, int norm_width,
+                                          float eps, float* residual, long long ldr, const float* next_w,
+                                          void* xw_out, long long ldxw, float* ss_out, long long ld_ss,
+                                          cudaStream_t stream) {
+  if (scale_parts && (n_parts <= 0 || ld_parts < M || norm_width <= 0 || !(eps > 0.f)))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05_fused: n_parts=%d ld_parts=%lld norm_width=%d eps=%g", n_parts, ld_parts,
+                  norm_width, (double)eps);
+  if (residual && swiglu8) return refuse(ST_BAD_SIZE, "gemm_tcgen05_fused: residual and SwiGLU epilogues exclude each other");
+  if (residual && (ldr < N || (next_w && (!xw_out || !ss_out || ldxw < N || ld_ss < M))))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05_fused: residual epilogue with incomplete arguments");
+  if (!residual && !C) return refuse(ST_BAD_SIZE, "gemm_tcgen05_fused: no output");
+  const GemmFuse fuse{scale_parts, n_parts, ld_parts, norm_width > 0 ? 1.f / (float)norm_width : 0.f, eps, residual,
+                      ldr, next_w, (bf16*)xw_out, ldxw, ss_out, ld_ss};
+  if (residual) {            // C is not written: the size checks of the plain entry must not trip over it
+    if (!C) C = residual;
+    ldc = N;
+  }
+  return gemm_entry(X, W, C, c_dtype, M, N, K, ldx, ldw, ldc, splits, workspace, workspace_bytes, err_flag, swiglu8,
+                    &fuse, stream);
 }
 
 // The width of the token tiles this file's entry point picks for a product of M tokens and N weight

@@ -56,6 +56,7 @@ class KernelLibrary:
         self.split_mixed_attention = True       # mixed steps: decoding requests to the keys-split kernel ...
         self.split_prefill_keys = True          # rows-split attention: the keys in slices when rows are few
         self.split_mixed_min_blocks = None      # ... when they make this many blocks (None: one per SM)
+        self.fuse_norms_into_products = True    # decode steps of up to 64 tokens: the blocks' norms inside the products
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
 
     @property
@@ -87,7 +88,8 @@ class KernelLibrary:
         """From now on every launch is followed by a CUDA event; ``end_timing`` turns the gaps between
         consecutive events into a table.  Kernels of one stream run one after the other, so the gap
         before a launch's event is that kernel's time (with its launch gap; no overlap between kernels
-        is possible while this is on: use it on eager steps, for shares, not for absolutes)."""
+        is possible while this is on: use it on eager steps, for shares, not for absolutes; launches that
+        go into a CUDA graph under capture are left out)."""
         start = torch.cuda.Event(enable_timing=True)
         start.record()
         self._timing = [("", start)]
@@ -104,7 +106,8 @@ class KernelLibrary:
 
     def _check(self, status: int, what: str):
         self.launches += 1
-        if getattr(self, "_timing", None) is not None and status == 0:
+        if getattr(self, "_timing", None) is not None and status == 0 \
+                and not torch.cuda.is_current_stream_capturing():      # a timed event cannot be recorded into a graph
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
             self._timing.append((what, ev))
@@ -294,6 +297,35 @@ class KernelLibrary:
             _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()),
             f"gemm_tn_tcgen05[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None else "gemm_tn_tcgen05")
 
+    FUSED_TOKENS = 64        # most tokens of a product that runs its norms inside itself
+
+    def gemm_tn_tcgen05_fused(self, a, w, out=None, swiglu8=False, scale_parts=None, norm_width=0, eps=0.0,
+                              residual=None, next_w=None, xw_out=None, ss_out=None):
+        """The tensor-core product of at most 64 tokens fused with the norms around it: the same contract
+        as gemm_tn_skinny_fused, except that the partial sums of squares lie as [parts, tokens]
+        (scale_parts: any row stride; ss_out: [ceil(N / 128), >= M])."""
+        M, K = a.shape
+        N = w.shape[0]
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or M > self.FUSED_TOKENS:
+            raise ShapeError(f"gemm_tcgen05_fused: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}")
+        if residual is None and (out is None or tuple(out.shape) != (M, N // 2 if swiglu8 else N)):
+            raise ShapeError("gemm_tcgen05_fused: out has the wrong shape")
+        if ss_out is not None and (ss_out.shape[0] < (N + 127) // 128 or ss_out.shape[1] < M):
+            raise ShapeError("gemm_tcgen05_fused: ss_out must be [ceil(N/128), >= M]")
+        ws, err = self._gemm_state(a.device)
+        self._check(self.lib.srlm_gemm_tn_tcgen05_fused(
+            _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype) if out is not None else DT_BF16, C.c_int(M),
+            C.c_int(N), C.c_int(K), C.c_longlong(a.stride(0)), C.c_longlong(w.stride(0)),
+            C.c_longlong(out.stride(0) if out is not None else N), C.c_int(self.gemm_splits(M, N, K)), _ptr(ws),
+            C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _ptr(scale_parts),
+            C.c_int(scale_parts.shape[0] if scale_parts is not None else 0),
+            C.c_longlong(scale_parts.stride(0) if scale_parts is not None else 0), C.c_int(norm_width), C.c_float(eps),
+            _ptr(residual), C.c_longlong(residual.stride(0) if residual is not None else 0), _ptr(next_w),
+            _ptr(xw_out), C.c_longlong(xw_out.stride(0) if xw_out is not None else 0), _ptr(ss_out),
+            C.c_longlong(ss_out.stride(0) if ss_out is not None else 0), _stream()),
+            f"gemm_tn_tcgen05_fused[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None
+            else "gemm_tn_tcgen05_fused")
+
     def gemm_dealt_tiles(self, M: int, N: int, K: int) -> int:
         """How many tiles of this product the persistent tensor-core kernel deals out by k-blocks
         (0: whole tiles only, or another kernel serves these sizes)."""
@@ -343,11 +375,16 @@ class KernelLibrary:
             f"gemm_tn_skinny_fused[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None
             else "gemm_tn_skinny_fused")
 
+    def fuses_in_skinny(self, T: int, w) -> bool:
+        """Whether a fused product of T tokens runs the weight-streaming kernel (else the tensor-core one)."""
+        return T <= min(8, self.skinny_max_tokens) and w.shape[0] <= self.skinny_max_rows \
+            and not self.force_tcgen05_gemm
+
     def can_fuse_norms(self, T: int, dtype, w) -> bool:
-        """Whether a product of T tokens with this weight may take the norm fusions of the skinny kernel."""
-        return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= min(8, self.skinny_max_tokens)
-                and w.shape[1] % 8 == 0 and w.shape[0] <= self.skinny_max_rows
-                and not (self.force_simt_gemm or self.force_tcgen05_gemm))
+        """Whether a product of T tokens with this weight may run the norms around it inside itself: the
+        weight-streaming kernel up to 8 tokens, the one-tile tensor-core kernel up to 64."""
+        return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= self.FUSED_TOKENS
+                and w.shape[1] % 8 == 0 and not self.force_simt_gemm and self.fuse_norms_into_products)
 
     def can_fuse_swiglu(self, a_dtype, w) -> bool:
         """Whether gemm(..., swiglu8=True) is offered for these operands (the tensor-core kernels only)."""

@@ -47,20 +47,35 @@ class Linear:
         """out = norm(x) . W^T for a lazily normalised input (see parts.base.NormedInput)."""
         if nx.ss_parts is None:
             ops.gemm(nx.xw, self.weight, out, swiglu8=swiglu8)
-        else:
+        elif ops.fuses_in_skinny(nx.xw.shape[0], self.weight):
             ops.gemm_tn_skinny_fused(nx.xw, self.weight, out, swiglu8=swiglu8, scale_parts=nx.ss_parts,
                                      norm_width=nx.width, eps=nx.eps)
+        else:
+            ops.gemm_tn_tcgen05_fused(nx.xw, self.weight, out, swiglu8=swiglu8, scale_parts=nx.ss_parts,
+                                      norm_width=nx.width, eps=nx.eps)
 
     def into_residual(self, ctx, x: torch.Tensor, residual: torch.Tensor, next_norm, slot: str, early: bool = True):
         """residual += x . W^T in the product's epilogue.  With ``next_norm`` (an RMSNorm part) the same
-        epilogue prepares the input of the part behind that norm and returns it as a NormedInput."""
+        epilogue prepares the input of the part behind that norm and returns it as a NormedInput.  Both
+        kernels that carry these fusions lay the partial sums of squares out as [parts, tokens]: 16
+        weight rows a part and 8 tokens wide (weight-streaming), or 128 rows a part (tensor cores); the
+        product that consumes them runs the same kernel, since both see the same number of tokens."""
         from .base import NormedInput
-        if next_norm is None:
-            ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, early=early)
-            return None
         T, N = x.shape[0], self.out_features
+        skinny = ops.fuses_in_skinny(T, self.weight)
+        if next_norm is None:
+            if skinny:
+                ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, early=early)
+            else:
+                ops.gemm_tn_tcgen05_fused(x, self.weight, residual=residual)
+            return None
         xw = ctx.workspace.get("fused.xw." + slot, T, N, ctx.dtype)
-        ss = ctx.workspace.get("fused.ss." + slot, (N + 15) // 16, 8, torch.float32, reserve=0)
-        ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw, ss_out=ss,
-                                 early=early)
+        if skinny:
+            ss = ctx.workspace.get("fused.ss." + slot, (N + 15) // 16, 8, torch.float32, reserve=0)
+            ops.gemm_tn_skinny_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw,
+                                     ss_out=ss, early=early)
+        else:
+            ss = ctx.workspace.get("fused.ss128." + slot, (N + 127) // 128, ops.FUSED_TOKENS, torch.float32, reserve=0)
+            ops.gemm_tn_tcgen05_fused(x, self.weight, residual=residual, next_w=next_norm.weight, xw_out=xw,
+                                      ss_out=ss)
         return NormedInput(xw, ss, next_norm.spec.size, next_norm.spec.eps)

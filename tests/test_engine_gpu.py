@@ -364,3 +364,46 @@ def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
         ref = plain_logits(folder_b, t)
         for p in range(len(t) - 8, len(t)):
             assert np.abs(out[True][(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("name", ["B", "G"])
+def test_norms_fused_into_products_of_up_to_64_tokens(name, tmp_path_factory):
+    """Steps of 9 to 64 tokens run their RMSNorms inside the tensor-core products: decode batches of a
+    dozen requests and short portions beside them, against the separate kernels and the plain logits."""
+    from conftest import make_folder
+    from safetyraise_lmengine_b200 import Engine
+    from safetyraise_lmengine_b200.kernels import ops
+    cfg, seed = TINY[name]
+    folder = make_folder(tmp_path_factory, cfg, seed, "fused64_" + name.lower())
+    rng = np.random.default_rng(23)
+    reqs = {f"r{i}": random_tokens(rng, 20 + 3 * i, cfg["vocab_size"]) for i in range(12)}
+    steps = [{"entries": [(r, t[:8], []) for r, t in reqs.items()]}]                       # 96 tokens: unfused
+    steps += [{"entries": [(r, t[8:12], [3]) for r, t in reqs.items()]}]                   # 48 tokens: fused
+    steps += [{"entries": [(r, t[12 + i:13 + i], [0]) for r, t in reqs.items()]} for i in range(8)]   # 12 tokens
+    out = {}
+    for fused in (True, False):
+        ops.fuse_norms_into_products = fused
+        try:
+            eng = Engine.from_folder(folder, dtype="bfloat16", page_size=16, num_pages=64, max_requests=12,
+                                     max_batch_tokens=512, options={"cuda_graphs": False})
+            ops.begin_timing()                       # (events between launches: not while a graph is recorded)
+            out[fused] = replay(eng, steps)
+            names = set(k.split("[")[0] for k in ops.end_timing())
+        finally:
+            ops.fuse_norms_into_products = True
+        assert ("gemm_tn_tcgen05_fused" in names) == fused, names
+    # the same steps with the decode steps replayed from CUDA graphs: the same bits
+    eng = Engine.from_folder(folder, dtype="bfloat16", page_size=16, num_pages=64, max_requests=12,
+                             max_batch_tokens=512)
+    recorded = replay(eng, steps)
+    assert eng.graph_replays >= 5
+    for k in recorded:
+        assert np.array_equal(recorded[k], out[True][k]), k
+    assert out[True].keys() == out[False].keys() and len(out[True]) == 12 * 9
+    for k in out[True]:
+        scale = np.abs(out[False][k]).max()
+        assert np.abs(out[True][k] - out[False][k]).max() <= 2e-2 * scale, k
+    for r, t in reqs.items():
+        ref = plain_logits(folder, t[:20])
+        for p in range(11, 20):
+            assert np.abs(out[True][(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()
