@@ -223,14 +223,22 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
   }
   __syncthreads();                        // the barriers are set up for every warp
-  pdl_wait();
-  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // When this kernel appends the step's keys itself, the kernel ahead (the projection) has written nothing
+  // that the producer warp reads: the batch's layout came before the step's first kernel, and the keys in
+  // the cache are those of earlier steps (a row of this step in a tile is stale either way and is replaced
+  // in shared memory below).  So the producer fetches its first tiles under the projection's tail.  It does
+  // not wait and does not trigger: the block lets its successor start only when its consumers have waited.
+  const bool ahead_of_wait = (HD == 64 || HD == 128 || HD == 256) && a.qkv != nullptr && warp == CONSUMERS;
+  if (!ahead_of_wait) {
+    pdl_wait();
+    pdl_trigger();
+  }
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
   const int rows_total = q_len * g;
   const int* table = a.block_table + (size_t)e * a.table_stride;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int first_key = a.window > 0 ? max(0, start - a.window + 1) : 0;
   const int slice_lo = z * a.kv_chunk, slice_hi = min(kv_len, slice_lo + a.kv_chunk);
