@@ -477,9 +477,12 @@ def run_mixed(args, shape: str, pk) -> dict:
                 steps.append((time.perf_counter() - t0, llm.last_step))
         return time.perf_counter() - t_all, steps, llm.metrics()
 
+    from safetyraise_lmengine_b200.kernels import ops
     one_pass(False)                                   # warm-up: graphs recorded, buffers sized
+    launches_before = ops.launches
     with ClockSampler() as clocks:
         seconds, steps, metrics = one_pass(True)
+    launches = ops.launches - launches_before         # (a replayed graph counts the launches it holds)
     per_token = linear_flops_per_token(spec)
     weight_bytes = eng.model.weight_bytes() - spec.vocab_size * spec.hidden_size * 2
     kv_bytes_per_token = eng.cache.bytes_per_page() // eng.cache.page_size
@@ -507,7 +510,7 @@ def run_mixed(args, shape: str, pk) -> dict:
         "config": dict(config_record(shape, cfg, len(spec.run_order), n_req, 0, "mixed"), prefill_chunk=chunk,
                        new_tokens=new, prompt_tokens=sum(lens)),
         "clocks": clocks.summary(),
-        "gpu_launches": None,
+        "gpu_launches": launches,
         "generated_tokens_per_second": round(n_req * new / seconds, 1),
         "seconds": round(seconds, 3),
         "decode_steps": {"steps": dec[1], "mean_ms": round(1000.0 * dec[0] / max(dec[1], 1), 3),

@@ -203,7 +203,8 @@ struct GemmArgs {
   int clustered;           // 1: the splits of a tile are one thread-block cluster (along z) and add their sums
                            //    through distributed shared memory; partial and tile_counters are not used
   int sk_tiles, sk_blocks; // persistent kernel: the k-blocks of the first sk_tiles tiles are dealt out evenly to
-                           //    the first sk_blocks blocks (0: every block takes whole tiles only)
+                           //    the first sk_blocks blocks, or pairs of blocks (0: every block takes whole tiles only)
+  int m_major;             // persistent kernel: tile t covers token tile t / (tiles along N); else t % (tiles along M)
   GemmFuse fuse;           // one-tile kernel only; all zero: none
 };
 
@@ -808,8 +809,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       PieceWalk walk(args, num_kb, total_tiles, walker, walkers);
       int t, kb_lo, kb_hi;
       while (ok && walk.next(t, kb_lo, kb_hi)) {
-        const int m0 = (t % tiles_m) * BN + (int)rank * (PAIR ? B_ROWS : 0);
-        const int n0 = (t / tiles_m) * TILE_N + (int)rank * BM;
+        const int m0 = (args.m_major ? t / tiles_n : t % tiles_m) * BN + (int)rank * (PAIR ? B_ROWS : 0);
+        const int n0 = (args.m_major ? t % tiles_n : t / tiles_m) * TILE_N + (int)rank * BM;
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES, j = it / STAGES;
           ok = mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 21);
@@ -875,11 +876,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const int sk_units = args.sk_tiles * num_kb;
     const int sk_base = args.sk_blocks ? sk_units / args.sk_blocks : 0;
     const int sk_rem = args.sk_blocks ? sk_units % args.sk_blocks : 0;
-    const int my_first_unit = sk_first_unit(blockIdx.x, sk_base, sk_rem);    // (no shares under PAIR: whole tiles)
+    const int my_first_unit = sk_first_unit(walker, sk_base, sk_rem);
+    // a pair shares its units; each of its blocks keeps its own 128 weight rows of every piece, in slots
+    // and under a counter of its own
+    const int slot_block = (int)blockIdx.x;
     constexpr size_t SLOT = (size_t)BN * BM;                // floats of a slot: [BN tokens][128 weight rows]
     for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
       const int b = local & 1;
-      const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * TILE_N + (int)rank * BM;
+      const int m0 = (args.m_major ? t / tiles_n : t % tiles_m) * BN;
+      const int n0 = (args.m_major ? t % tiles_n : t / tiles_m) * TILE_N + (int)rank * BM;
       ok = mbar_wait(&acc_full[b], (local >> 1) & 1, args.err_flag, 24);
       if (!ok) break;
       tcgen05_fence_after();
@@ -889,7 +894,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       if (!whole) {
         // this block's sums of a part of the tile's k-blocks -> its slot (0: the piece its share begins
         // with, 1: the piece it ends with)
-        float* mine = args.partial + (2 * (size_t)blockIdx.x + (t * num_kb + kb_lo == my_first_unit ? 0 : 1)) * SLOT;
+        float* mine = args.partial + (2 * (size_t)slot_block + (t * num_kb + kb_lo == my_first_unit ? 0 : 1)) * SLOT;
 #pragma unroll 1
         for (int c = 0; c < BN; c += SLAB) {
           uint32_t v[SLAB];
@@ -909,56 +914,125 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (tid_e == 0) {
-          const int prev = atomicAdd(&args.tile_counters[t], 1);
+          int* counter = args.tile_counters + (PAIR ? 2 * t + (int)rank : t);
+          const int prev = atomicAdd(counter, 1);
           const int last = prev == part_last - part_first;
-          if (last) args.tile_counters[t] = 0;              // clean for the next product
+          if (last) *counter = 0;                           // clean for the next product
           *last_flag = last;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (!*last_flag) continue;                          // somebody else finishes this tile
         __threadfence();
+        // The parts of the blocks part_first .. part_last, added in that order, straight from the workspace
+        // to C.  A thread takes an item of 8 sums of one token: 8 consecutive weight rows, or through SwiGLU 4
+        // gate rows and the 4 up rows of the same features; four items at a time, with the loads of up to
+        // three parts of each in flight together.
+        const int np = part_last - part_first + 1;
+        constexpr int IPT = BM / 8;                         // items per token
+        const int items = min(BN, args.M - m0) * IPT;
+        const int n_limit = (args.swiglu8 ? args.N / 2 : args.N) - c0;
+        auto slot_of = [&](int pb) {
+          const int which = sk_first_unit(pb, sk_base, sk_rem) >= t * num_kb ? 0 : 1;
+          const size_t blk = PAIR ? 2 * (size_t)pb + rank : (size_t)pb;
+          return args.partial + (2 * blk + which) * SLOT;
+        };
+        constexpr int U = 4, P = 3;
+#pragma unroll 1
+        for (int base = tid_e; base < items; base += 128 * U) {
+          float acc[U][8];
+          size_t off[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int idx = min(base + u * 128, items - 1), v = idx % IPT;
+            off[u] = (size_t)(idx / IPT) * BM + (args.swiglu8 ? (v >> 1) * 16 + (v & 1) * 4 : v * 8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+          }
+          const int second = args.swiglu8 ? 8 : 4;          // floats from an item's first four sums to its other four
+#pragma unroll 1
+          for (int p0 = 0; p0 < np; p0 += P) {
+            float4 got[P][U][2];
+#pragma unroll
+            for (int q = 0; q < P; ++q) {
+              if (p0 + q < np) {
+                const float* src = slot_of(part_first + p0 + q);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                  got[q][u][0] = __ldcg(reinterpret_cast<const float4*>(src + off[u]));
+                  got[q][u][1] = __ldcg(reinterpret_cast<const float4*>(src + off[u] + second));
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < P; ++q) {
+              if (p0 + q < np) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                  acc[u][0] += got[q][u][0].x; acc[u][1] += got[q][u][0].y;
+                  acc[u][2] += got[q][u][0].z; acc[u][3] += got[q][u][0].w;
+                  acc[u][4] += got[q][u][1].x; acc[u][5] += got[q][u][1].y;
+                  acc[u][6] += got[q][u][1].z; acc[u][7] += got[q][u][1].w;
+                }
+              }
+            }
+          }
+          auto two = [](float lo, float hi) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+            return *reinterpret_cast<const uint32_t*>(&v);
+          };
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int idx = base + u * 128;
+            if (idx < items) {
+              const int j = idx / IPT, v = idx % IPT;
+              if (args.swiglu8) {
+                const int col = (v >> 1) * 8 + (v & 1) * 4;          // first of 4 columns of C within the tile
+                const float h[4] = {silu_stable(acc[u][0]) * acc[u][4], silu_stable(acc[u][1]) * acc[u][5],
+                                    silu_stable(acc[u][2]) * acc[u][6], silu_stable(acc[u][3]) * acc[u][7]};
+                uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + j) * args.ldc + c0 + col) * esize;
+                if (vec_ok && col + 4 <= n_limit) {
+                  if (args.c_is_f32) *reinterpret_cast<float4*>(dst) = make_float4(h[0], h[1], h[2], h[3]);
+                  else *reinterpret_cast<uint2*>(dst) = make_uint2(two(h[0], h[1]), two(h[2], h[3]));
+                } else {
+                  for (int e = 0; e < 4 && col + e < n_limit; ++e) {
+                    if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = h[e];
+                    else reinterpret_cast<bf16*>(dst)[e] = __float2bfloat16_rn(h[e]);
+                  }
+                }
+              } else {
+                const int col = v * 8;                               // first of 8 columns of C within the tile
+                uint8_t* dst = reinterpret_cast<uint8_t*>(args.C) + ((size_t)(m0 + j) * args.ldc + c0 + col) * esize;
+                if (vec_ok && col + 8 <= n_limit) {
+                  if (args.c_is_f32) {
+                    reinterpret_cast<float4*>(dst)[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+                    reinterpret_cast<float4*>(dst)[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+                  } else {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(two(acc[u][0], acc[u][1]), two(acc[u][2], acc[u][3]),
+                                                                two(acc[u][4], acc[u][5]), two(acc[u][6], acc[u][7]));
+                  }
+                } else {
+                  for (int e = 0; e < 8 && col + e < n_limit; ++e) {
+                    if (args.c_is_f32) reinterpret_cast<float*>(dst)[e] = acc[u][e];
+                    else reinterpret_cast<bf16*>(dst)[e] = __float2bfloat16_rn(acc[u][e]);
+                  }
+                }
+              }
+            }
+          }
+        }
+        continue;
       }
 #pragma unroll 1
       for (int c = 0; c < BN; c += SLAB, slab_turn ^= 1) {
         uint32_t v[SLAB];
-        if (whole) {
-          tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
-          tmem_load_wait();
-          if (c + SLAB >= BN) {                             // everything of this tile has left TMEM
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) acc_drained<PAIR>(&acc_empty[b]);
-          }
-          if (m0 + c >= args.M) continue;                   // slab beyond the last token (same for all warps)
-        } else {
-          if (m0 + c >= args.M) continue;
-          // the parts of the blocks part_first .. part_last, added in that order; the next part's
-          // loads are in flight while this one is added
-          float acc[SLAB];
-#pragma unroll
-          for (int j = 0; j < SLAB; ++j) acc[j] = 0.f;
-          auto part_of = [&](int pb) {
-            const int which = sk_first_unit(pb, sk_base, sk_rem) >= t * num_kb ? 0 : 1;
-            return args.partial + (2 * (size_t)pb + which) * SLOT + (size_t)c * BM + lane_base + lane;
-          };
-          float got[SLAB], ahead[SLAB];
-          const float* src = part_of(part_first);
-#pragma unroll
-          for (int j = 0; j < SLAB; ++j) got[j] = __ldcg(src + (size_t)j * BM);
-          for (int pb = part_first; pb <= part_last; ++pb) {
-            if (pb < part_last) {
-              const float* nxt = part_of(pb + 1);
-#pragma unroll
-              for (int j = 0; j < SLAB; ++j) ahead[j] = __ldcg(nxt + (size_t)j * BM);
-            }
-#pragma unroll
-            for (int j = 0; j < SLAB; ++j) acc[j] += got[j];
-#pragma unroll
-            for (int j = 0; j < SLAB; ++j) got[j] = ahead[j];
-          }
-#pragma unroll
-          for (int j = 0; j < SLAB; ++j) v[j] = __float_as_uint(acc[j]);
+        tmem_load<SLAB>(tmem_base + ((uint32_t)lane_base << 16) + b * BN + c, v);
+        tmem_load_wait();
+        if (c + SLAB >= BN) {                               // everything of this tile has left TMEM
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) acc_drained<PAIR>(&acc_empty[b]);
         }
+        if (m0 + c >= args.M) continue;                     // slab beyond the last token (same for all warps)
         uint8_t* sl = slab + slab_turn * SLAB * SLAB_ROW;
         // D[n, m] -> slab[m][column of C]
         if (args.swiglu8) {
@@ -1174,8 +1248,22 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
 
 // The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x BN tokens, a cluster of
 // two blocks per tile, whole tiles only.  mx: the token map with boxes of BN / 2 rows.
+// How many tiles the pair form deals out by k-blocks: all of them, when they would occupy at most 70 % of the
+// pairs in their one round and every pair still gets 96 k-blocks or more.  The tiles are then numbered with
+// the weight tile running fastest (m_major), so that the pairs that work on the same weight rows for different
+// token tiles are half the GPU apart and walk their k-blocks in step: what one fetched is in the L2 for the other.
+// Measured at 512 tokens (40 tiles on 74 pairs): down projection of 5120 x 17408 92.7 -> 82.8 us, of 5120 x
+// 25600 132.4 -> 114.2 us; with shorter shares the trip of the parts through the workspace, all at the end,
+// costs more than the idle pairs (5120 x 5120: 33.7 -> 42.3 us; 6144 x 4096: 28.5 -> 41.4 us).
+static int dealt_pair_tiles(int tiles, int num_kb, int pairs) {
+  if (pairs <= 1 || tiles >= pairs || tiles * 10 > pairs * 7) return 0;
+  if ((long long)tiles * num_kb / pairs < 96 || 2 * tiles > 16384) return 0;
+  return tiles;
+}
+
 template <int BN, int STAGES>
-static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, long long ws_bytes,
+                       cudaStream_t stream) {
   constexpr int SMEM = STAGES * (BM * BK * 2 + (BN / 2) * BK * 2) + 2 * 32 * (BM * 4 + 16) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static_assert(SMEM <= 232448, "shared memory of a block");
   static bool configured = false;
@@ -1190,11 +1278,23 @@ static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmA
     configured = true;
   }
   const int tiles = ((a.N + 2 * BM - 1) / (2 * BM)) * ((a.M + BN - 1) / BN);
-  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   GemmArgs b = a;
-  b.sk_tiles = b.sk_blocks = 0;
-  // whole tiles only: dealing the left-over tiles' k-blocks out to the pairs measured slower more often
-  // than faster (1,024 tokens: QKV 68.5 against 56.1 us; 4,096 tokens: down 265 against 277 us)
+  b.sk_tiles = b.sk_blocks = b.m_major = 0;
+  // More tiles than pairs: whole tiles only (dealing the left-over tiles' k-blocks out to the pairs measured
+  // slower more often than faster: 1,024 tokens: QKV 68.5 against 56.1 us; 4,096 tokens: down 265 against
+  // 277 us).  Fewer: see dealt_pair_tiles.
+  static const bool whole_only = getenv("SRLM_GEMM_STREAMK") && !atoi(getenv("SRLM_GEMM_STREAMK"));
+  const long long slots_bytes = 2ll * sm_count * BN * BM * 4;
+  if (!whole_only && b.partial && b.tile_counters && ws_bytes >= 65536 + slots_bytes) {
+    const int sk = dealt_pair_tiles(tiles, (a.K + BK - 1) / BK, sm_count / 2);
+    if (sk > 0) {
+      pairs = sm_count / 2;
+      b.sk_tiles = sk;
+      b.sk_blocks = pairs;
+      b.m_major = 1;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(GEMM_THREADS);
@@ -1299,7 +1399,7 @@ static int gemm_entry(const void* X, const void* W, void* C, int c_dtype, int M,
     if (!off && bn == 256 && !pair_off) {
       const CUtensorMap* mx128 = &mx128_copy;
       if (!cached_map(&mx128_copy, X, M, K, ldx, 128, false)) return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
-      return launch_pair<256, 6>(mw, mx128, a, stream);
+      return launch_pair<256, 6>(mw, mx128, a, workspace_bytes, stream);
     }
 
     if (!off)
@@ -1369,7 +1469,8 @@ extern "C" int srlm_gemm_tcgen05_dealt_tiles(int M, int N, int K) {
   if (bn < 128) return 0;
   if (sm_count <= 0) return 0;
   static const bool pair_off = getenv("SRLM_GEMM_PAIR") && !atoi(getenv("SRLM_GEMM_PAIR"));
-  if (bn == 256 && !pair_off) return 0;       // pairs of SMs on tiles of 256 x 256: whole tiles
+  if (bn == 256 && !pair_off)                 // pairs of SMs on tiles of 256 x 256
+    return dealt_pair_tiles(((N + 2 * BM - 1) / (2 * BM)) * ((M + 255) / 256), (K + BK - 1) / BK, sm_count / 2);
   return dealt_tiles(((N + BM - 1) / BM) * ((M + bn - 1) / bn), (K + BK - 1) / BK, sm_count);
 }
 

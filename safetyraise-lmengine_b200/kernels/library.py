@@ -263,7 +263,12 @@ class KernelLibrary:
             elif M <= 64:
                 sp = min(200 // max(1, tiles), total_kb // 8, 8)
             else:
-                sp = min(200 // max(1, tiles), total_kb // 8, 4)
+                # tiles of 128 tokens, two blocks to an SM: up to about 256 blocks run as one round (clusters
+                # of 3 or 4 do not pack the GPCs to the last slot: 288 blocks measured a round more).  At 256
+                # tokens, 14B sizes: down projection 61.5 -> 53.3 us with 3 splits instead of 2 (80 tiles),
+                # 8B sizes: 36.1 -> 31.3 us with 4 instead of 3 (64 tiles); 512 tokens, 8B: 58.4 -> 51.8 us
+                # with 2 splits of 128 tiles
+                sp = min(256 // max(1, tiles), total_kb // 8, 4)
             sp = max(1, sp)
             while sp > 8 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
                 sp -= 1

@@ -302,8 +302,10 @@ def test_gemm_tn_tcgen05(M, N, K, splits, odt):
     # token tiles of 128 whose tiles do not fill the last round: the persistent kernel deals the k-blocks of
     # the left-over tiles out evenly, parts of a tile meet in the workspace and are added in a fixed order
     (128, 22000, 4096, True), (128, 24576, 2048, True), (100, 24000, 2304, True),
-    # a few hundred tokens and a narrow output: two rounds of 128 x 128 tiles, or one of pairs' tiles (chosen)
-    (512, 6000, 2048, False), (500, 5120, 6400, False), (512, 4096, 1024, False),
+    # a few hundred tokens and a narrow output: two rounds of 128 x 128 tiles, or one of pairs' tiles (chosen);
+    # tiles for at most 70 % of the pairs and a long K: their k-blocks are dealt out evenly to all pairs
+    (512, 6000, 2048, False), (500, 5120, 6400, False), (512, 4096, 1024, False), (512, 5000, 14400, True),
+    (400, 6100, 12296, True), (260, 6300, 16008, True),
     # token tiles of 256: a pair of SMs (cta_group::2) per tile of 256 weight rows x 256 tokens; ragged
     # token counts, a last tile whose second half lies beyond the weight rows, K no multiple of 64
     (2048, 6144, 4096, False), (900, 6144, 2048, False), (1100, 24576, 1792, False), (1300, 4224, 3000, False),
