@@ -224,12 +224,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   __syncthreads();                        // the barriers are set up for every warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // When this kernel appends the step's keys itself, the kernel ahead (the projection) has written nothing
-  // that the producer warp reads: the batch's layout came before the step's first kernel, and the keys in
-  // the cache are those of earlier steps (a row of this step in a tile is stale either way and is replaced
-  // in shared memory below).  So the producer fetches its first tiles under the projection's tail.  It does
-  // not wait and does not trigger: the block lets its successor start only when its consumers have waited.
-  const bool ahead_of_wait = (HD == 64 || HD == 128 || HD == 256) && a.qkv != nullptr && warp == CONSUMERS;
+  // When this kernel appends the step's keys itself, no kernel of this step has written anything that the
+  // producer warp reads: the batch's layout came before the step's first kernel, and the keys in the cache
+  // are those of earlier steps (a row of this step in a tile is stale either way and is replaced in shared
+  // memory below).  So the producer fetches its first tiles under the projection's tail.  It does not wait
+  // and does not trigger: the block lets its successor start only when its consumers have waited.  A step
+  // that reads keys which another kernel of the same step appended (write_kv == 0) must not run ahead: the
+  // products between that kernel and this one let their successors start before they have waited
+  // themselves, so it may still be running.
+  const bool ahead_of_wait = (HD == 64 || HD == 128 || HD == 256) && a.qkv != nullptr && a.write_kv &&
+                             warp == CONSUMERS;
   if (!ahead_of_wait) {
     pdl_wait();
     pdl_trigger();

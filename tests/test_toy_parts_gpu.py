@@ -520,3 +520,95 @@ def test_toy_window_attention_gives_pages_back_and_matches_plain(dtype):
         assert eng.cache.audit() == 0 and eng.cache.free_pages() == 20
     taken, reused = eng.cache.reuse_counts()
     assert reused > 0 and taken > 20
+
+
+# ---------------------------------------------------------------------------
+# A fourth toy architecture, data only: the framework's own parts in a run order whose last step runs
+# layer 0's weights again and reads the keys and values that the first step wrote (it appends nothing).
+# ---------------------------------------------------------------------------
+SHARED_CONFIG = {
+    "architectures": ["ToySharedForCausalLM"], "model_type": "toy",
+    "num_hidden_layers": 2, "hidden_size": 72, "num_attention_heads": 2, "num_key_value_heads": 1,
+    "head_dim": 64, "intermediate_size": 104, "vocab_size": 110, "rope_theta": 8000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 256,
+}
+
+
+def define_shared_toy():
+    import dataclasses
+
+    from safetyraise_lmengine_b200 import ARCHITECTURES, register_architecture
+    from safetyraise_lmengine_b200.config import qwen3
+    from safetyraise_lmengine_b200.config.spec import RunStep
+    from safetyraise_lmengine_b200.parts.model import DecoderModel
+    if "ToySharedForCausalLM" in ARCHITECTURES:
+        return
+
+    def read_spec(cfg):
+        base = qwen3.read_spec(dict(cfg, architectures=["Qwen3ForCausalLM"], model_type="qwen3"))
+        order = (RunStep(0, 0), RunStep(1, 1), RunStep(0, 0, writes_cache=False))
+        return dataclasses.replace(base, architecture="ToySharedForCausalLM", run_order=order)
+
+    register_architecture("ToySharedForCausalLM", read_spec, lambda spec, mctx, src: DecoderModel(spec, mctx, src))
+
+
+def plain_shared_logits(w, tokens):
+    cfg = SHARED_CONFIG
+    w = {k: v.float().numpy().astype(np.float64) for k, v in w.items()}
+    nq, nkv, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    T = len(tokens)
+    pos = np.arange(T)
+    x = P.embedding(w["model.embed_tokens.weight"], tokens)
+    p = "model.layers.0."
+    # the first step's keys and values, as it leaves them in the cache
+    n1 = P.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+    k = P.rope(P.rms_norm(P.linear(n1, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, hd),
+                          w[p + "self_attn.k_norm.weight"], eps), pos, cfg["rope_theta"], hd)
+    v = P.linear(n1, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, hd)
+    x = P.block(x, pos, w, 0, cfg)
+    x = P.block(x, pos, w, 1, cfg)
+    # the last step: layer 0's weights on the new hidden state, queries only
+    n1 = P.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+    q = P.rope(P.rms_norm(P.linear(n1, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, hd),
+                          w[p + "self_attn.q_norm.weight"], eps), pos, cfg["rope_theta"], hd)
+    r = x + P.linear(P.causal_attention(q, k, v).reshape(T, nq * hd), w[p + "self_attn.o_proj.weight"])
+    n2 = P.rms_norm(r, w[p + "post_attention_layernorm.weight"], eps)
+    x = r + P.feed_forward_part(n2, w, p + "mlp.")
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_run_step_reads_the_cache_that_another_step_wrote(dtype):
+    """Three steps over two layers; the third attends over the first one's keys, this step's among them
+    (written a few kernels earlier in the same forward pass), in prompts, portions and decode steps that are
+    replayed from CUDA graphs."""
+    from helpers import TOL, cut_bulk_tail, cut_portions, cut_whole, replay
+    from safetyraise_lmengine_b200 import Engine, spec_from_config
+    from safetyraise_lmengine_b200.parts.model import tensor_decls
+    from safetyraise_lmengine_b200.weights.random_init import RandomWeights
+    define_shared_toy()
+    spec = spec_from_config(SHARED_CONFIG)
+    src = RandomWeights(tensor_decls(spec), seed=5)
+    w = {n: src.get(n) for n in src.names()}
+    rng = np.random.default_rng(4)
+    toks = [int(t) for t in rng.integers(0, 110, size=90)]
+    ref = plain_shared_logits(w, toks)
+    # the shared keys matter: with the last step attending over keys of its own the logits are others
+    w64 = {k: v.float().numpy().astype(np.float64) for k, v in w.items()}
+    x, pos = P.embedding(w64["model.embed_tokens.weight"], toks), np.arange(len(toks))
+    for layer in (0, 1, 0):
+        x = P.block(x, pos, w64, layer, SHARED_CONFIG)
+    own = P.linear(P.rms_norm(x, w64["model.norm.weight"], 1e-6), w64["model.embed_tokens.weight"])
+    assert np.abs(own - ref).max() > 0.05 * np.abs(ref).max()
+    eng = Engine.from_source(SHARED_CONFIG, src, dtype=dtype, page_size=16, num_pages=24, max_requests=2,
+                             max_batch_tokens=128)
+    paged = [g for g in eng.cache.groups if g.kind == "paged_all"][0]
+    assert paged.entries == (0, 1)                       # two cache entries for three steps
+    for steps in (cut_whole("x", toks), cut_bulk_tail("x", toks, 32), cut_portions("x", toks)):
+        got = replay(eng, steps)
+        rows = np.stack([got[("x", p)] for p in range(len(toks))])
+        err = np.abs(rows - ref).max(axis=1) / np.abs(ref).max()
+        assert err.max() <= TOL[dtype], f"first wrong position {int(np.argmax(err > TOL[dtype]))}"
+    assert eng.cache.audit() == 0
+    if dtype == "bfloat16":
+        assert eng.graph_replays >= 20
