@@ -32,6 +32,7 @@
 
 #include <cstdlib>
 #include <map>
+#include <atomic>
 #include <mutex>
 #include <tuple>
 
@@ -1321,9 +1322,12 @@ using namespace srlm;
 // at the start; float32 partials [splits, tiles, token tile, 128] from byte 65536 on, any contents.  err_flag: one int the kernel sets to a nonzero code if a wait ran out.
 // The SM count of the current device (0 if it cannot be had).
 static int device_sms() {
+  static std::atomic<int> known[64];            // per device; 0: not asked yet
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (dev >= 0 && dev < 64 && (sms = known[dev].load(std::memory_order_relaxed)) > 0) return sms;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (dev >= 0 && dev < 64) known[dev].store(sms, std::memory_order_relaxed);
   return sms;
 }
 

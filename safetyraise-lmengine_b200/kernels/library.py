@@ -8,6 +8,7 @@ current stream, so the calls can be recorded into a CUDA graph.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 from typing import Optional
 
 import torch
@@ -35,7 +36,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return C.c_void_p(t.data_ptr())
 
 
+# torch.cuda.current_stream() builds a Stream object through several Python layers (3.4 us measured, a
+# third of a launch's host cost); the two calls below are what it ends in.
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_CURRENT_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current CUDA stream of the current device (the capturing one while a graph is recorded)."""
+    if _RAW_STREAM is not None and _CURRENT_DEVICE is not None:
+        return C.c_void_p(_RAW_STREAM(_CURRENT_DEVICE()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -227,6 +237,7 @@ class KernelLibrary:
     BN256_MIN_TILES = 96
 
     @staticmethod
+    @functools.lru_cache(maxsize=4096)
     def gemm_token_tile(M: int, N: int) -> int:
         """The width of the token tiles of the tensor-core product of M tokens and N weight rows (the rule
         of token_tile in gemm_tcgen05.cu, where its reasons and measurements stand)."""
@@ -241,6 +252,7 @@ class KernelLibrary:
         return 256 if 4 * rounds256 < 3 * rounds128 else 128
 
     @staticmethod
+    @functools.lru_cache(maxsize=4096)
     def gemm_splits(M: int, N: int, K: int) -> int:
         """How many ways to split K: the number of blocks should fill whole waves of the SMs
         (192 tiles alone would leave the second wave two thirds empty), each split keeping at

@@ -80,20 +80,28 @@ class Workspace:
     def __init__(self, device, max_tokens: int):
         self.device, self.max_tokens = device, max_tokens
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}     # (name, width, dtype, rows) -> buf[:rows]: slicing costs 1.5 us
         self.generation = 0      # grows whenever a buffer moves: recorded CUDA graphs are stale then
 
     def get(self, name: str, rows: int, width: int, dtype: torch.dtype, reserve=None) -> torch.Tensor:
         """A [rows, width] view of the buffer ``name``; the buffer is made for ``reserve`` rows
         (default: the most tokens a step may hold) and grows if a step ever needs more."""
+        view = self._views.get((name, width, dtype, rows))
+        if view is not None:
+            return view
         key = (name, width, dtype)
         buf = self._bufs.get(key)
         cap = max(rows, self.max_tokens if reserve is None else reserve, 1)
         if buf is None or buf.shape[0] < rows:
             if buf is not None:
                 self.generation += 1
+                self._views = {k: v for k, v in self._views.items() if k[:3] != key}
             buf = torch.empty((cap, width), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:rows]
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[(name, width, dtype, rows)] = buf[:rows]
+        return view
 
 
 # Words of a step's status buffer (int32, on the device; zero = fine).  The engine reads them back
