@@ -18,7 +18,8 @@
 // tokens with a double-buffered accumulator; the k-blocks of tiles that do not
 // fill a round may be dealt out evenly.  (3) Persistent pairs: two SMs (a cluster
 // of two blocks) on tiles of 256 weight rows x 256 tokens with cta_group::2 MMAs,
-// for many tokens.
+// for many tokens; when there are tiles for only part of the pairs and K is long,
+// all k-blocks are dealt out evenly to all pairs.
 //
 // Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the
 // MMAs, warps 2-5 run the epilogue.  Every wait on an mbarrier is bounded: when
@@ -1247,8 +1248,6 @@ static int launch_persistent(const CUtensorMap* mw, const CUtensorMap* mx, const
   return launched();
 }
 
-// The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x BN tokens, a cluster of
-// two blocks per tile, whole tiles only.  mx: the token map with boxes of BN / 2 rows.
 // How many tiles the pair form deals out by k-blocks: all of them, when they would occupy at most 70 % of the
 // pairs in their one round and every pair still gets 96 k-blocks or more.  The tiles are then numbered with
 // the weight tile running fastest (m_major), so that the pairs that work on the same weight rows for different
@@ -1262,6 +1261,9 @@ static int dealt_pair_tiles(int tiles, int num_kb, int pairs) {
   return tiles;
 }
 
+// The pair form of the persistent kernel (see PAIR there): tiles of 256 weight rows x BN tokens, a cluster of
+// two blocks per tile; whole tiles, or all k-blocks dealt out (dealt_pair_tiles).  mx: the token map with boxes
+// of BN / 2 rows.
 template <int BN, int STAGES>
 static int launch_pair(const CUtensorMap* mw, const CUtensorMap* mx, const GemmArgs& a, long long ws_bytes,
                        cudaStream_t stream) {
