@@ -170,7 +170,7 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-// Optional fusions of the one-tile kernel with the norms around a product (decode steps of 9 to 64 tokens;
+// Optional fusions of the one-tile kernel with the norms around a product (decode steps of 9 to 128 tokens;
 // the same scheme as the weight-streaming kernel's, gemm_skinny.cu):
 //  * scale_parts [n_parts][ld_parts]: the tokens X are (residual * norm weight) in bfloat16, not yet divided
 //    by their RMS; the product is scaled per token by rsqrt(sum_p scale_parts[p][token] / norm_width + eps).
@@ -270,7 +270,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  float* ss_half = reinterpret_cast<float*>(tmem_slot + 4);     // [2][64]: halves of the tokens' sums of squares
+  float* ss_half = reinterpret_cast<float*>(tmem_slot + 4);     // [2][64] halves of the tokens' sums of squares
+                                                                //   (token tiles of 128: [128] whole sums)
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -336,7 +337,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       into[j] = r;
     }
   };
-  const bool fused = BN <= 64 && (f.scale_parts != nullptr || f.residual != nullptr);
+  const bool fused = BN <= 128 && (f.scale_parts != nullptr || f.residual != nullptr);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -394,11 +395,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (fused) {
       if (f.scale_parts) {
         // thread t adds every second part of token t % 64 (neighbouring threads, neighbouring tokens); the two
-        // halves meet in shared memory behind the barrier below
-        const int t = threadIdx.x - 64, m = t & 63;
+        // halves meet in shared memory behind the barrier below.  With 128 tokens a thread adds all parts of one.
+        const int t = threadIdx.x - 64, m = BN > 64 ? t : (t & 63);
+        const int q0 = BN > 64 ? 0 : (t >> 6), dq = BN > 64 ? 1 : 2;
         float p = 0.f;
         if (m < rows)
-          for (int q = t >> 6; q < f.n_parts; q += 2) p += __ldg(f.scale_parts + (size_t)q * f.ld_parts + m0 + m);
+          for (int q = q0; q < f.n_parts; q += dq) p += __ldg(f.scale_parts + (size_t)q * f.ld_parts + m0 + m);
         ss_half[t] = p;
       }
       if (f.residual && !split) residual_rows(held, m_first);   // (splits in global memory: the owner is not known yet)
@@ -500,7 +502,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---- rows of the slab -> C or the residual stream, with the norms around the product folded in ----
     // 1 / RMS of token m: the halves are added in one order
     auto scale_of = [&](const int m) {
-      return f.scale_parts ? rsqrtf((ss_half[m] + ss_half[64 + m]) * f.inv_width + f.eps) : 1.f;
+      return f.scale_parts ? rsqrtf((BN > 64 ? ss_half[m] : ss_half[m] + ss_half[64 + m]) * f.inv_width + f.eps) : 1.f;
     };
     const int esize = args.c_is_f32 ? 4 : 2;
     const bool vec_ok = (args.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.C) & 15) == 0);
@@ -1371,8 +1373,8 @@ static int gemm_entry(const void* X, const void* W, void* C, int c_dtype, int M,
   const int bn = token_tile(M, N, device_sms());
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, kb_per_split, nullptr, nullptr, swiglu8 ? 1 : 0, 0};
   if (fuse) {
-    if (bn > 64)
-      return refuse(ST_BAD_SIZE, "gemm_tcgen05: the norm fusions take at most 64 tokens, got %d", M);
+    if (bn > 128)
+      return refuse(ST_BAD_SIZE, "gemm_tcgen05: the norm fusions take at most 128 tokens, got %d", M);
     a.fuse = *fuse;
   }
   // up to 8 splits (the portable cluster size) add their sums inside a thread-block cluster and need no
@@ -1392,7 +1394,8 @@ static int gemm_entry(const void* X, const void* W, void* C, int c_dtype, int M,
   const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;
   if (!cached_map(&mw_copy, W, N, K, ldw, BM, true) || !cached_map(&mx_copy, X, M, K, ldx, bn, false))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05: cuTensorMapEncodeTiled refused the operands");
-  if (splits == 1 && bn >= 128) {     // many tokens: the persistent kernel (SRLM_GEMM_PERSISTENT=0: one tile per block)
+  if (splits == 1 && bn >= 128 && !fuse) {   // many tokens: the persistent kernel (SRLM_GEMM_PERSISTENT=0: one tile per
+                                             // block); the norm fusions live in the one-tile kernel
     static const bool off = getenv("SRLM_GEMM_PERSISTENT") && !atoi(getenv("SRLM_GEMM_PERSISTENT"));
     // SRLM_GEMM_STREAMK=0: whole tiles only
     static const bool whole_only = getenv("SRLM_GEMM_STREAMK") && !atoi(getenv("SRLM_GEMM_STREAMK"));
@@ -1433,7 +1436,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
                     nullptr, stream);
 }
 
-// The same product for 9 to 64 tokens fused with the norms around it (see GemmFuse).  scale_parts may be
+// The same product for 9 to 128 tokens fused with the norms around it (see GemmFuse).  scale_parts may be
 // null (X is already normalised); residual may be null (the product is stored to C, possibly through
 // SwiGLU); with residual C is not written and may be null.
 extern "C" int srlm_gemm_tn_tcgen05_fused(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,

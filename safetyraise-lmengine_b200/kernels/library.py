@@ -66,7 +66,7 @@ class KernelLibrary:
         self.split_mixed_attention = True       # mixed steps: decoding requests to the keys-split kernel ...
         self.split_prefill_keys = True          # rows-split attention: the keys in slices when rows are few
         self.split_mixed_min_blocks = None      # ... when they make this many blocks (None: one per SM)
-        self.fuse_norms_into_products = True    # decode steps of up to 64 tokens: the blocks' norms inside the products
+        self.fuse_norms_into_products = True    # steps of up to 128 tokens: the blocks' norms inside the products
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
 
     @property
@@ -314,11 +314,11 @@ class KernelLibrary:
             _ptr(ws), C.c_longlong(ws.numel()), _ptr(err), C.c_int(int(swiglu8)), _stream()),
             f"gemm_tn_tcgen05[{M}x{N}x{K}]" if getattr(self, "_timing", None) is not None else "gemm_tn_tcgen05")
 
-    FUSED_TOKENS = 64        # most tokens of a product that runs its norms inside itself
+    FUSED_TOKENS = 128       # most tokens of a product that runs its norms inside itself
 
     def gemm_tn_tcgen05_fused(self, a, w, out=None, swiglu8=False, scale_parts=None, norm_width=0, eps=0.0,
                               residual=None, next_w=None, xw_out=None, ss_out=None):
-        """The tensor-core product of at most 64 tokens fused with the norms around it: the same contract
+        """The tensor-core product of at most 128 tokens fused with the norms around it: the same contract
         as gemm_tn_skinny_fused, except that the partial sums of squares lie as [parts, tokens]
         (scale_parts: any row stride; ss_out: [ceil(N / 128), >= M])."""
         M, K = a.shape
@@ -399,7 +399,7 @@ class KernelLibrary:
 
     def can_fuse_norms(self, T: int, dtype, w) -> bool:
         """Whether a product of T tokens with this weight may run the norms around it inside itself: the
-        weight-streaming kernel up to 8 tokens, the one-tile tensor-core kernel up to 64."""
+        weight-streaming kernel up to 8 tokens, the one-tile tensor-core kernel up to 128."""
         return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= self.FUSED_TOKENS
                 and w.shape[1] % 8 == 0 and not self.force_simt_gemm and self.fuse_norms_into_products)
 

@@ -367,8 +367,8 @@ def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
 
 
 @pytest.mark.parametrize("name", ["B", "G"])
-def test_norms_fused_into_products_of_up_to_64_tokens(name, tmp_path_factory):
-    """Steps of 9 to 64 tokens run their RMSNorms inside the tensor-core products: decode batches of a
+def test_norms_fused_into_products_of_up_to_128_tokens(name, tmp_path_factory):
+    """Steps of 9 to 128 tokens run their RMSNorms inside the tensor-core products: decode batches of a
     dozen requests and short portions beside them, against the separate kernels and the plain logits."""
     from conftest import make_folder
     from safetyraise_lmengine_b200 import Engine
@@ -376,10 +376,11 @@ def test_norms_fused_into_products_of_up_to_64_tokens(name, tmp_path_factory):
     cfg, seed = TINY[name]
     folder = make_folder(tmp_path_factory, cfg, seed, "fused64_" + name.lower())
     rng = np.random.default_rng(23)
-    reqs = {f"r{i}": random_tokens(rng, 20 + 3 * i, cfg["vocab_size"]) for i in range(12)}
-    steps = [{"entries": [(r, t[:8], []) for r, t in reqs.items()]}]                       # 96 tokens: unfused
-    steps += [{"entries": [(r, t[8:12], [3]) for r, t in reqs.items()]}]                   # 48 tokens: fused
-    steps += [{"entries": [(r, t[12 + i:13 + i], [0]) for r, t in reqs.items()]} for i in range(8)]   # 12 tokens
+    reqs = {f"r{i}": random_tokens(rng, 35 + 3 * i, cfg["vocab_size"]) for i in range(12)}
+    steps = [{"entries": [(r, t[:15], []) for r, t in reqs.items()]}]                      # 180 tokens: unfused
+    steps += [{"entries": [(r, t[15:23], [7]) for r, t in reqs.items()]}]                  # 96 tokens: fused
+    steps += [{"entries": [(r, t[23:27], [3]) for r, t in reqs.items()]}]                  # 48 tokens: fused
+    steps += [{"entries": [(r, t[27 + i:28 + i], [0]) for r, t in reqs.items()]} for i in range(8)]   # 12 tokens
     out = {}
     for fused in (True, False):
         ops.fuse_norms_into_products = fused
@@ -399,11 +400,11 @@ def test_norms_fused_into_products_of_up_to_64_tokens(name, tmp_path_factory):
     assert eng.graph_replays >= 5
     for k in recorded:
         assert np.array_equal(recorded[k], out[True][k]), k
-    assert out[True].keys() == out[False].keys() and len(out[True]) == 12 * 9
+    assert out[True].keys() == out[False].keys() and len(out[True]) == 12 * 10
     for k in out[True]:
         scale = np.abs(out[False][k]).max()
         assert np.abs(out[True][k] - out[False][k]).max() <= 2e-2 * scale, k
     for r, t in reqs.items():
-        ref = plain_logits(folder, t[:20])
-        for p in range(11, 20):
+        ref = plain_logits(folder, t[:35])
+        for p in [22, 26] + list(range(27, 35)):
             assert np.abs(out[True][(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()
