@@ -56,8 +56,10 @@ class KernelLibrary:
         self.force_simt_gemm = False   # tests: run the float32 FMA twin in place of the tensor cores
         self.force_simt_attention = False
         self.force_tcgen05_gemm = False
-        # the weight-streaming kernel serves products of at most this many tokens and weight rows
-        self.skinny_max_tokens = 8
+        # The weight-streaming (mma.sync) kernel serves products of at most this many tokens and weight rows.
+        # 0: none -- the one-tile tensor-core kernel with its K splits in a cluster streams the weights faster
+        # at every token count (a layer's four products at 8 tokens: 70.8 against 82.8 us); 8 brings it back.
+        self.skinny_max_tokens = 0
         self.skinny_max_rows = 1 << 30
         self.force_cp_async_decode = False
         self.cluster_decode_merge = True        # slices of decode attention merged in a thread-block cluster
@@ -285,15 +287,11 @@ class KernelLibrary:
             while sp > 8 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
                 sp -= 1
             return sp
-        best, best_eff = 1, 0.0
-        for s in range(1, 17):
-            if s > 1 and (total_kb // s < 4 or 65536 + s * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES):
-                break
-            blocks = tiles * s
-            eff = blocks / (-(-blocks // KernelLibrary.SMS) * KernelLibrary.SMS)
-            if eff > best_eff + 0.04:
-                best, best_eff = s, eff
-        return best
+        # Up to 16 tokens three blocks share an SM (444 at a time); splits up to the cluster's 8.  Measured on
+        # B200 at 16 tokens, 8B layer sizes (QKV / O / gate-up / down): 4-8 / 6-8 / 2 / 6-8 splits are best
+        # (11.6 / 9.6 / 32.1 / 19.7 us; gate/up unsplit 35.0 us, in 3 splits 37.5 us; down in 9 splits through
+        # the workspace 23.4 us).
+        return max(1, min(444 // max(1, tiles), total_kb // 8, 8))
 
     def gemm_tn_tcgen05(self, a, w, out, splits=None, swiglu8=False):
         """out[M,N] = a[M,K] @ w[N,K]^T, bfloat16 operands, tcgen05 tensor cores, float32 accumulation.

@@ -341,9 +341,12 @@ def test_a_long_prompt_in_portions_then_decoding(dtype, long_prompt_folder):
     assert eng.cache.audit() == 0
 
 
-def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
+@pytest.mark.parametrize("streaming_tokens", [0, 8])
+def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b, streaming_tokens):
     """Decode steps of up to 8 tokens run their RMSNorms inside the products around them; the same
-    steps with the fusion switched off must give the same logits within rounding."""
+    steps with the fusion switched off must give the same logits within rounding.  Once on the
+    tensor-core kernel (the default), once on the weight-streaming kernel that may stand in for it."""
+    from safetyraise_lmengine_b200.kernels import ops
     cfg, _ = TINY["B"]
     rng = np.random.default_rng(13)
     reqs = {r: random_tokens(rng, n, cfg["vocab_size"]) for r, n in (("a", 30), ("b", 47), ("c", 12))}
@@ -352,9 +355,17 @@ def test_norms_fused_into_products_agree_with_the_separate_kernels(folder_b):
     steps[-1]["end"] = list(reqs)
     steps += [{"entries": [("d", reqs["a"][:5], [0, 4]), ("e", reqs["b"][:3], [2])]}]      # 8 prompt tokens
     out = {}
-    for fused in (True, False):
-        eng = build(folder_b, "bfloat16", options={"unfused_norms": not fused, "cuda_graphs": False})
-        out[fused] = replay(eng, steps)
+    keep, ops.skinny_max_tokens = ops.skinny_max_tokens, streaming_tokens
+    try:
+        for fused in (True, False):
+            eng = build(folder_b, "bfloat16", options={"unfused_norms": not fused, "cuda_graphs": False})
+            ops.begin_timing()
+            out[fused] = replay(eng, steps)
+            names = set(k.split("[")[0] for k in ops.end_timing())
+            assert (("gemm_tn_skinny_fused" if streaming_tokens else "gemm_tn_tcgen05_fused") in names) == fused, names
+            assert ("gemm_tn_skinny" in names or "gemm_tn_skinny_fused" in names) == bool(streaming_tokens), names
+    finally:
+        ops.skinny_max_tokens = keep
     assert out[True].keys() == out[False].keys() and len(out[True]) == 3 * 8 + 3
     for k in out[True]:
         scale = np.abs(out[False][k]).max()
