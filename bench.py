@@ -539,6 +539,8 @@ def main() -> int:
     ap.add_argument("--skip-extras", action="store_true", help="only the default decode measurement")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
+    ap.add_argument("--streaming-kernel", action="store_true",
+                    help="steps of up to 8 tokens on the weight-streaming mma.sync kernel instead of the tensor-core one")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the block of --steps steps until this much is timed (0: one block, for profilers)")
     args = ap.parse_args()
@@ -549,6 +551,9 @@ def main() -> int:
         return 2
     args.warmup = max(args.warmup, 3)
     workload = args.workload or ("mixed" if args.shape == "14b" else "decode")
+    if args.streaming_kernel:
+        from safetyraise_lmengine_b200.kernels import ops
+        ops.skinny_max_tokens = 8
     pk = peaks()
     out = run_mixed(args, args.shape, pk) if workload == "mixed" else run_decode(args, args.shape, pk)
     print(json.dumps(out))
