@@ -284,6 +284,8 @@ class KernelLibrary:
                 # with 2 splits of 128 tiles
                 sp = min(256 // max(1, tiles), total_kb // 8, 4)
             sp = max(1, sp)
+            if M <= 64 and sp == 1 and 148 < tiles and 2 * tiles <= 444 and total_kb >= 16:
+                sp = 2        # three blocks of a shallower ring an SM (the kernel picks it by the block count)
             while sp > 8 and 65536 + sp * tiles * 128 * bn * 4 > KernelLibrary.GEMM_WS_BYTES:
                 sp -= 1
             return sp
