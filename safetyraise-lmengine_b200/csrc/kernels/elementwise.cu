@@ -8,6 +8,20 @@
 
 namespace srlm {
 
+__global__ void patch_words_kernel(int* __restrict__ words, long long words_len, const int* __restrict__ pairs,
+                                   const int* __restrict__ src, int src_len, int n, int* __restrict__ flag) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int to = pairs[2 * i], from = pairs[2 * i + 1];
+  if (to < 0 || to >= words_len || from < 0 || from >= src_len) {
+    atomicExch(flag, 1);
+    return;
+  }
+  words[to] = src[from];
+}
+
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                     float* __restrict__ out, int H, int vocab, int* __restrict__ bad) {
@@ -241,6 +255,18 @@ extern "C" int srlm_residual_add(float* residual, const void* delta, int act_dty
   if (n <= 0) return ST_OK;
   SRLM_DISPATCH_ACT(act_dtype, TA, (residual_add_kernel<TA><<<flat_grid((size_t)n, 256), 256, 0, stream>>>(
       residual, (const TA*)delta, (size_t)n)));
+  return launched();
+}
+
+// words[pairs[2 i]] = src[pairs[2 i + 1]] for i < n: token ids that a step takes from what the step before
+// it sampled, while the host has not read them yet.  A source index outside [0, src_len) or a destination
+// outside [0, words_len) is skipped and raises the flag (the host checks too).
+extern "C" int srlm_patch_words(int* words, long long words_len, const int* pairs, const int* src, int src_len,
+                                int n, int* flag, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (!words || !pairs || !src || !flag) return refuse(ST_BAD_SIZE, "patch_words: a null argument");
+  launch_pdl(patch_words_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, words, words_len, pairs, src, src_len,
+             n, flag);
   return launched();
 }
 

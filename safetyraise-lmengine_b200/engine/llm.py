@@ -40,6 +40,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     device: str = "cuda:0"
     plan_ahead: bool = True                # the next decode step's host work runs while the device works
+    launch_ahead: bool = True              # ... and the step itself is queued before this one's tokens are read
 
     def validate(self) -> None:            # src/engine/scheduler.rs:124-141
         for name in ("max_context", "max_active", "queue_capacity", "prefill_chunk", "max_request_ms",
@@ -83,6 +84,9 @@ class LLM:
         self._ids = itertools.count(1)
         self.failed = self.cancelled = 0
         self._prepared = None          # (plan, PreparedStep, open token places) of a step laid out ahead
+        self._inflight = None          # (plan, PreparedStep, sampler rows) of a step queued on the device ahead
+        self.steps_ahead = 0           # steps that were queued on the device before the step ahead of them was read
+        self.steps_dropped = 0         # ... and those of them that were taken back (a stop token, a fault, a cancel)
         self.last_step: Optional[dict] = None   # what the last step ran: {"starts": [...], "counts": [...]} per entry
 
     # ---- construction ---------------------------------------------------------
@@ -205,6 +209,53 @@ class LLM:
         self._prepared = (nxt, prep, later)
         return True
 
+    def _drop_ahead(self) -> None:
+        """Takes back whatever was done for the step after the current one: a step laid out ahead, or
+        one already queued on the device (it is waited for, then revoked: lengths, pages and state as
+        before it; the fault words it may have raised are of no interest)."""
+        self._discard_prepared()
+        if self._inflight is None:
+            return
+        plan, prep, _ = self._inflight
+        self._inflight = None
+        self.steps_dropped += 1
+        with torch.cuda.device(self.engine.mctx.device):
+            torch.cuda.synchronize()
+            self.engine.revoke(prep)
+            self.sampler.clear_words()
+        for p in plan:
+            self.scheduler.rollback(p.request_id)
+
+    def _may_launch_ahead(self, states) -> bool:
+        """The step laid out ahead may be queued before this step's tokens are read: its token ids are
+        taken on the device, so nothing of it may need them on the host -- no repetition penalty (its
+        history) -- and what a dropped step leaves behind must be what ``Engine.revoke`` restores."""
+        if not self.config.launch_ahead or self._prepared is None:
+            return False
+        if any(s.request.sampling.repetition_penalty != 1.0 for s in states):
+            return False
+        nxt, _, later = self._prepared
+        return len(later) == len(nxt)            # every entry decodes the token being sampled now
+
+    def _launch_ahead(self, sampled) -> None:
+        """Queues the step that was laid out ahead behind this step's sampler: its open token ids are
+        filled on the device from the sampler's rows."""
+        nxt, prep, later = self._prepared
+        self._prepared = None
+        row_of = {p.request_id: k for k, p in enumerate(sampled)}
+        try:
+            logits = self.engine.run(prep, [(entry, index, row_of[rid]) for entry, index, rid in later])
+        except EngineError:
+            for p in nxt:                              # planned normally at the next turn
+                self.scheduler.rollback(p.request_id)
+            return
+        states = [self._live[p.request_id] for p in nxt if p.want_logits]
+        rows = self.sampler.launch(
+            logits, [s.request.sampling for s in states], [s.seed for s in states],
+            [len(s.tokens) - s.usage.prompt_tokens + 1 for s in states], [s.tokens for s in states])
+        self._inflight = (nxt, prep, rows)
+        self.steps_ahead += 1
+
     def step(self, on_token: Optional[Callable[[int, int, int], None]] = None) -> bool:
         """One scheduler turn: interruptions, plan, one engine step, sampling.  False when idle."""
         now = time.monotonic()
@@ -212,53 +263,62 @@ class LLM:
             reason = FINISH_CANCELLED if st.cancelled else \
                 FINISH_DEADLINE if st.deadline_at is not None and now >= st.deadline_at else None
             if reason is not None:
-                self._discard_prepared()
+                self._drop_ahead()
                 self._finish(rid, reason)
-        if self._prepared is not None:
-            plan, prep, _ = self._prepared
-            self._prepared = None
+        if self._inflight is not None:                # queued on the device during the turn before
+            plan, prep, rows = self._inflight
+            self._inflight = None
+            sampled = [p for p in plan if p.want_logits]
+            states = [self._live[p.request_id] for p in sampled]
         else:
-            if not self.scheduler.has_work():
-                return False
-            plan, preempted = self.scheduler.plan()
-            for rid in preempted:
-                self._live[rid].usage.preemptions += 1
-            if not plan:
-                return self.scheduler.has_work() and bool(self._live)
-            entries = []
+            if self._prepared is not None:
+                plan, prep, _ = self._prepared
+                self._prepared = None
+            else:
+                if not self.scheduler.has_work():
+                    return False
+                plan, preempted = self.scheduler.plan()
+                for rid in preempted:
+                    self._live[rid].usage.preemptions += 1
+                if not plan:
+                    return self.scheduler.has_work() and bool(self._live)
+                entries = []
+                for p in plan:
+                    st = self._live[p.request_id]
+                    entries.append(StepEntry(p.slot, st.tokens[p.start:p.start + p.count],
+                                             [p.count - 1] if p.want_logits else []))
+                try:
+                    prep = self.engine.prepare(entries)
+                except EngineError as e:
+                    self._fail_plan(plan, e)
+                    return True
             for p in plan:
                 st = self._live[p.request_id]
-                entries.append(StepEntry(p.slot, st.tokens[p.start:p.start + p.count],
-                                         [p.count - 1] if p.want_logits else []))
+                if st.first_step_at is None:
+                    st.first_step_at = now
+                    st.usage.queue_ms = (now - st.submitted_at) * 1000.0
             try:
-                prep = self.engine.prepare(entries)
+                logits = self.engine.run(prep)
             except EngineError as e:
                 self._fail_plan(plan, e)
                 return True
-        for p in plan:
-            st = self._live[p.request_id]
-            if st.first_step_at is None:
-                st.first_step_at = now
-                st.usage.queue_ms = (now - st.submitted_at) * 1000.0
-        try:
-            logits = self.engine.run(prep)
-        except EngineError as e:
-            self._fail_plan(plan, e)
-            return True
+            sampled = [p for p in plan if p.want_logits]
+            states = [self._live[p.request_id] for p in sampled]
+            rows = self.sampler.launch(
+                logits, [s.request.sampling for s in states], [s.seed for s in states],
+                [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
         self.last_step = {"starts": [p.start for p in plan], "counts": [p.count for p in plan]}
-        sampled = [p for p in plan if p.want_logits]
-        states = [self._live[p.request_id] for p in sampled]
-        rows = self.sampler.launch(
-            logits, [s.request.sampling for s in states], [s.seed for s in states],
-            [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
         ahead = self._plan_ahead(plan, sampled, states)        # overlaps the device's work
+        if ahead and self._may_launch_ahead(states):
+            rows = self.sampler.snapshot(rows)                 # this step's tokens and words, read below
+            self._launch_ahead(sampled)                        # the next step waits on the device already
         tokens = self.sampler.collect(rows)                     # waits for the device; the fault words come along
         fault = self.engine.fault_of(self.sampler.last_words)
         if fault is not None:
             # the step's result cannot be trusted: none of its tokens is published, every request of
             # the step ends with an error and gives its pages and its slot back
             # (src/engine/scheduler.rs:882-895)
-            self._discard_prepared()
+            self._drop_ahead()
             prep.state_snapshot = None
             self._fail_plan(plan, fault)
             return True
@@ -267,7 +327,7 @@ class LLM:
                 self.scheduler.advance(p.request_id, p.count)
         stopped = [p.request_id for p, tok in zip(sampled, tokens) if tok in self.eos]
         if ahead and stopped:
-            self._discard_prepared()                   # a stop token changes who decodes next
+            self._drop_ahead()                         # a stop token changes who decodes next
         by_rid = {}
         for p, st, tok in zip(sampled, states, tokens):
             rid = p.request_id

@@ -23,7 +23,8 @@ import torch
 from ..cache.manager import CacheManager
 from ..config.registry import architecture_of, read_config_json
 from ..errors import ConfigError, ResourceExhausted, ShapeError, StepFailed, Unavailable
-from ..parts.base import FAULT_LOGITS, FAULT_NAMES, STATUS_WORDS, ModelContext, StepContext, Workspace
+from ..parts.base import (FAULT_LOGITS, FAULT_NAMES, FAULT_TOKEN, STATUS_WORDS, ModelContext, StepContext,
+                          Workspace)
 from ..weights.safetensors_io import WeightFolder
 
 DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16,
@@ -368,17 +369,39 @@ class Engine:
         """Gives back what a prepared step reserved; nothing of it ran."""
         self.discard_reservation(prep.entries, prep.starts)
 
-    def launch(self, prep: PreparedStep) -> torch.Tensor:
+    def launch(self, prep: PreparedStep, patch: Optional[Sequence[tuple]] = None) -> torch.Tensor:
         """The device half without its book-keeping: one copy of the layout, then the forward.  The
-        lengths do not move; ``commit`` or ``revoke`` must follow."""
-        if prep.missing:
+        lengths do not move; ``commit`` or ``revoke`` must follow.
+
+        patch: token ids left open as LATER that the device fills in itself, as (entry, index, row) --
+        token ``index`` of entry ``entry`` is the token that the sampler bound to this engine's status
+        buffer wrote for its row ``row`` (the step before this one, which the host has not read yet)."""
+        patch = list(patch or ())
+        if prep.missing != len(patch):
             self.discard(prep)
-            raise ShapeError(f"{prep.missing} token ids of the prepared step were never set")
+            raise ShapeError(f"{prep.missing} token ids of the prepared step were never set "
+                             f"({len(patch)} are taken on the device)")
         try:
             with torch.cuda.device(self.mctx.device):
                 from ..kernels import ops
                 ops.bind_error_flag(self.status[:1])
+                if patch:
+                    # the pairs (word of the token id, sampler row) ride behind the layout in the same copy
+                    at = _round_up(prep.words, 4)
+                    h = prep.host if prep.host is not None else prep.pair[0].numpy()
+                    if at + 2 * len(patch) > h.shape[0]:
+                        raise ShapeError("the step's layout leaves no room for the token pairs")
+                    for k, (entry, index, row) in enumerate(patch):
+                        word = prep.token_at[entry] + index
+                        if h[word] != LATER or not 0 <= row < self.cache.max_requests:
+                            raise ShapeError(f"token {index} of entry {entry} is not open, or row {row} does not exist")
+                        h[at + 2 * k], h[at + 2 * k + 1] = word, row
+                    layout_words, prep.words = prep.words, at + 2 * len(patch)
                 ctx = self._upload(prep)
+                if patch:
+                    prep.words = layout_words
+                    ops.patch_words(self._meta_dev, self._meta_dev[at:at + 2 * len(patch)],
+                                    self.status[STATUS_WORDS:], len(patch), self.status[FAULT_TOKEN:FAULT_TOKEN + 1])
                 if self.cache.state_pools:
                     # fixed-size state cannot be truncated: keep what the step's slots held
                     # (src/engine/state.rs:222-224 clones the whole state for the same reason)
@@ -423,12 +446,12 @@ class Engine:
         what = [f"{FAULT_NAMES.get(i, 'fault word %d' % i)} ({w})" for i, w in enumerate(words) if w]
         return StepFailed("the step failed and nothing of it was kept: " + "; ".join(what), words)
 
-    def run(self, prep: PreparedStep) -> torch.Tensor:
+    def run(self, prep: PreparedStep, patch: Optional[Sequence[tuple]] = None) -> torch.Tensor:
         """The device half for a caller that reads the step's fault words itself, together with what
         it reads back anyway (the generation loop: ``Sampler.collect``): launches, advances the
         lengths at once so that the next step can be laid out while this one runs, and returns.
-        A raised word then means ``revoke``."""
-        logits = self.launch(prep)
+        A raised word then means ``revoke``.  patch: see ``launch``."""
+        logits = self.launch(prep, patch)
         self.commit(prep)
         return logits
 

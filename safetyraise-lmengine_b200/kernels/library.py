@@ -152,6 +152,15 @@ class KernelLibrary:
         self._check(self.lib.srlm_cast(_ptr(src), dtype_code(src.dtype), _ptr(dst), dtype_code(dst.dtype),
                                        C.c_longlong(src.numel()), _stream()), "cast")
 
+    def patch_words(self, words, pairs, src, n, flag):
+        """words[pairs[2 i]] = src[pairs[2 i + 1]] for i < n, all int32 on the device: token ids that a step
+        takes from what the step before it sampled, before the host has read them.  An index outside its
+        tensor is skipped and raises flag[0]."""
+        if any(t.dtype != torch.int32 for t in (words, pairs, src, flag)) or pairs.numel() < 2 * n:
+            raise ShapeError("patch_words: int32 tensors, two words a pair")
+        self._check(self.lib.srlm_patch_words(_ptr(words), C.c_longlong(words.numel()), _ptr(pairs), _ptr(src),
+                                              C.c_int(src.numel()), C.c_int(n), _ptr(flag), _stream()), "patch_words")
+
     def check_finite(self, a, b, flag):
         """flag[0] = 1 if any element of a (+ b, same shape, when given) is NaN or infinite; a float32."""
         if a.dtype != torch.float32 or (b is not None and b.numel() != a.numel()):

@@ -68,7 +68,10 @@ class Sampler:
             self._status[:self._words].copy_(old[:self._words])
             self.bad = self._status[FAULT_LOGITS:FAULT_LOGITS + 1]
         self._cap = rows
-        self._host = torch.empty(5 * rows, dtype=torch.float32, pin_memory=True)
+        # the rows' parameters go through pinned buffers taken in turn: a launch may be queued while the copy
+        # of the launch before it has not run yet; each buffer waits for the event behind its last copy
+        self._hosts = [[torch.empty(5 * rows, dtype=torch.float32, pin_memory=True), None] for _ in range(3)]
+        self._host_turn = 0
         self._dev = torch.empty(5 * rows, dtype=torch.float32, device=self.device)
         self._out = self._status[self._words:self._words + rows]
         self._scratch = None               # [rows, vocab] float32, made when a row is first sampled
@@ -80,12 +83,34 @@ class Sampler:
         """logits [n, V] float32 on the device; one token id per row, as Python ints."""
         return self.collect(self.launch(logits, params, seeds, indices, histories))
 
-    def collect(self, n: int) -> List[int]:
+    def collect(self, n) -> List[int]:
         """The tokens of the last launch(): waits for the device and reads them back, the fault words
-        with them (``last_words``; the caller decides what a raised word means)."""
-        got = self._status[:self._words + n].tolist()
+        with them (``last_words``; the caller decides what a raised word means).  ``n``: the number of
+        rows that launch() returned, or what snapshot() returned for them."""
+        if isinstance(n, tuple):
+            host, event, rows = n
+            event.synchronize()
+            got = host[:self._words + rows].tolist()
+        else:
+            got = self._status[:self._words + n].tolist()
         self.last_words = got[:self._words]
         return got[self._words:]
+
+    def snapshot(self, n: int):
+        """Copies the fault words and the ``n`` tokens of the last launch() to pinned host memory behind
+        what the stream holds so far, so that collect() of the returned handle waits for that copy alone
+        and further work may be queued behind it meanwhile (it may overwrite the words and the tokens).
+        At most two handles are alive at a time."""
+        ring = self.__dict__.setdefault("_snapshots", [])
+        need = self._words + self._cap
+        if not ring or ring[0].numel() < need:
+            ring[:] = [torch.empty(need, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self._snapshot_turn = (getattr(self, "_snapshot_turn", 0) + 1) % len(ring)
+        host = ring[self._snapshot_turn]
+        host[:self._words + n].copy_(self._status[:self._words + n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return host, event, n
 
     def clear_words(self) -> None:
         self._status[:self._words].zero_()
@@ -102,7 +127,11 @@ class Sampler:
         if all(p.is_greedy for p in params):
             ops.argmax(logits, self._out[:n], self.bad)
             return n
-        h = self._host.numpy()
+        self._host_turn = (self._host_turn + 1) % len(self._hosts)
+        pair = self._hosts[self._host_turn]
+        if pair[1] is not None:
+            pair[1].synchronize()
+        h = pair[0].numpy()
         c = self._cap
         for i, p in enumerate(params):
             h[i] = p.temperature
@@ -110,8 +139,9 @@ class Sampler:
             h[2 * c + i] = p.repetition_penalty
             h[3 * c + i] = uniform_for(seeds[i], indices[i]) if p.temperature > 0 else 0.0
         h[4 * c:4 * c + n].view(np.int32)[:] = [p.top_k for p in params]
-        # the previous call ended by reading its tokens back, so its copy has left the pinned buffer
-        self._dev.copy_(self._host, non_blocking=True)
+        self._dev.copy_(pair[0], non_blocking=True)
+        pair[1] = torch.cuda.Event()
+        pair[1].record()
         d = self._dev
         hist = offs = None
         if any(p.repetition_penalty != 1.0 for p in params):

@@ -119,12 +119,14 @@ def plain_greedy(folder, prompt, n):
     return toks[len(prompt):]
 
 
-@pytest.mark.parametrize("plan_ahead", [True, False])
-def test_generation_ends_a_failed_steps_requests_with_error(folder_b, plan_ahead):
+@pytest.mark.parametrize("plan_ahead, launch_ahead", [(True, True), (True, False), (False, False)])
+def test_generation_ends_a_failed_steps_requests_with_error(folder_b, plan_ahead, launch_ahead):
     """The scheduler's side (src/engine/scheduler.rs:882-895): the requests of the failed step end
-    with ``error``, their pages and slots come back, and the engine goes on serving."""
+    with ``error``, their pages and slots come back, and the engine goes on serving.  With a step
+    queued ahead, the step that was already on the device when the weight broke is a sound one: its
+    tokens are published, and the step queued behind the failed one is taken back."""
     from safetyraise_lmengine_b200 import GenerationRequest, SamplingParams
-    llm = llm_for(folder_b, plan_ahead=plan_ahead)
+    llm = llm_for(folder_b, plan_ahead=plan_ahead, launch_ahead=launch_ahead)
     eng = llm.engine
     vocab = TINY["B"][0]["vocab_size"]
     rng = np.random.default_rng(2)
@@ -137,10 +139,16 @@ def test_generation_ends_a_failed_steps_requests_with_error(folder_b, plan_ahead
     for _ in range(6):                                       # prompts are in, decoding has begun
         llm.step(lambda rid, tok, i: seen.append((rid, tok)))
     assert len(seen) >= 4
+    torch.cuda.synchronize()                                 # (a step queued ahead has run with sound weights)
     down[5].fill_(float("nan"))                              # the failure, made on the host
     published = len(seen)
     llm.run_until_idle(lambda rid, tok, i: seen.append((rid, tok)))
-    assert len(seen) == published                            # no token of a failed step is published
+    # no token of a failed step is published; the sound step that was on the device already publishes its two
+    assert len(seen) == published + (2 if launch_ahead else 0)
+    for rid, p in zip(ids, prompts):
+        got = [tok for r, tok in seen if r == rid]
+        assert got == plain_greedy(folder_b, p, 12)[:len(got)]
+    assert llm.steps_dropped == (1 if launch_ahead else 0)
     for rid in ids:
         res = llm.take_result(rid)
         assert res.finish_reason == "error" and "non-finite" in res.error

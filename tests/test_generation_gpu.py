@@ -68,13 +68,13 @@ def test_planning_ahead_changes_no_token_and_no_count(folder_b):
     rng = np.random.default_rng(5)
     prompts = [random_tokens(rng, n, 100) for n in (9, 14, 3, 21, 6, 12)]
 
-    def run(ahead, stop, **kw):
+    def run(ahead, stop, penalty=1.2, **kw):
         llm = make_llm(folder_b, "float32", plan_ahead=ahead, **kw)
         llm.eos = set(stop)
         ids = []
         for i, pr in enumerate(prompts):
             sp = SamplingParams(temperature=0.0 if i % 2 == 0 else 0.9, top_k=20, top_p=0.9, seed=100 + i,
-                                repetition_penalty=1.0 if i % 3 else 1.2, max_new_tokens=10 + i)
+                                repetition_penalty=1.0 if i % 3 else penalty, max_new_tokens=10 + i)
             ids.append(llm.submit(GenerationRequest(pr, sp)))
         seen = []
         llm.run_until_idle(lambda rid, tok, n: seen.append((rid, tok, n)))
@@ -99,6 +99,52 @@ def test_planning_ahead_changes_no_token_and_no_count(folder_b):
     ahead_p, _, m1, llm = run(True, stop, num_pages=14)
     assert ahead_p == plain_p and m1 == m0
     assert [t for t, _, _ in plain_p] == [t for t, _, _ in plain_s]
+    # (a repetition penalty needs the token before it on the host: steps with one are not queued ahead; the
+    # runs above queue steps ahead only once the requests with a penalty have ended)
+    # without penalties the next step is queued on the device before this step's tokens are read; a stop
+    # token among them takes the queued step back; the tokens, their order and the counters stay the same
+    for kw in ({"max_active": 6}, {}, {"num_pages": 14}):
+        plain_q, seen0, m0, _ = run(False, (), penalty=1.0, **kw)
+        stop = {plain_q[1][0][4], plain_q[3][0][7]}
+        for stops in ((), stop):
+            plain_q, seen0, m0, _ = run(False, stops, penalty=1.0, **kw)
+            ahead_q, seen1, m1, llm = run(True, stops, penalty=1.0, **kw)
+            off_q, seen2, m2, off = run(True, stops, penalty=1.0, launch_ahead=False, **kw)
+            assert ahead_q == plain_q == off_q and m1 == m0 == m2, (kw, stops)
+            if "num_pages" not in kw:      # (with preemptions the order in which tokens are published may differ)
+                assert seen1 == seen0 == seen2, (kw, stops)
+            assert llm.steps_ahead > 3 and off.steps_ahead == 0
+            if not stops:
+                assert llm.steps_dropped == 0
+            elif "max_active" in kw:                   # all six decode together when the stop tokens come
+                assert llm.steps_dropped > 0
+
+
+def test_a_cancelled_request_takes_the_step_queued_ahead_back(folder_b):
+    """While three requests decode, each turn queues the next step on the device before it reads the
+    current one.  A request cancelled between two turns is part of the step in flight: that step is waited
+    for and taken back (lengths, pages), the request ends, the others go on from where they were and
+    produce the tokens they would have produced alone."""
+    from safetyraise_lmengine_b200 import SamplingParams
+    from safetyraise_lmengine_b200.engine.scheduler import GenerationRequest
+    cfg, _ = TINY["B"]
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (7, 12, 5)]
+    llm = make_llm(folder_b, "float32")
+    llm.eos = set()
+    ids = [llm.submit(GenerationRequest(p, SamplingParams(temperature=0.0, max_new_tokens=14))) for p in prompts]
+    while llm.steps_ahead < 3:
+        assert llm.step()
+    assert llm._inflight is not None and llm.steps_dropped == 0
+    llm.cancel(ids[1])
+    llm.run_until_idle()
+    assert llm.steps_dropped == 1
+    res = [llm.take_result(i) for i in ids]
+    assert [r.finish_reason for r in res] == ["length", "cancelled", "length"]
+    for p, r in zip(prompts, res):
+        check_greedy_path(folder_b, p, r.tokens, "float32")
+    assert len(res[0].tokens) == len(res[2].tokens) == 14 and 0 < len(res[1].tokens) < 14
+    assert llm.engine.cache.audit() == 0 and llm.engine.cache.free_pages() == 64
 
 
 def test_preemption_and_recompute_give_the_same_tokens(folder_b):
