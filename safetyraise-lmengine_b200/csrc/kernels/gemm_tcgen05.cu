@@ -72,18 +72,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the flag) if the barrier did not flip in time.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
+// Bounded wait.  Returns false (and raises the flag) if the barrier did not flip within `limit` cycles.
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, int* err_flag, int code,
+                                              long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       atomicExch(err_flag, code);
       return false;
     }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag, int code) {
+  return mbar_wait_for(bar, parity, err_flag, code, WAIT_CYCLES);
+}
+
+// One thread waits, with the wait of the pipelines below and a limit of its own, on a barrier that nobody
+// arrives at: the wait runs out, the flag is raised, the kernel ends normally.  For the test of the way from a
+// wait that ran out to the host; nothing else launches it.
+__global__ void wait_probe_kernel(int* err_flag, long long limit, int code) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_for(&bar, 0, err_flag, code, limit);
   }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -1469,6 +1485,15 @@ extern "C" int srlm_gemm_tn_tcgen05_fused(const void* X, const void* W, void* C,
   }
   return gemm_entry(X, W, C, c_dtype, M, N, K, ldx, ldw, ldc, splits, workspace, workspace_bytes, err_flag, swiglu8,
                     &fuse, stream);
+}
+
+// Launches wait_probe_kernel: a wait of at most limit_cycles (refused beyond 2e9, about a second) that runs out
+// and writes `code` to err_flag.
+extern "C" int srlm_wait_probe(int* err_flag, long long limit_cycles, int code, cudaStream_t stream) {
+  if (!err_flag || limit_cycles <= 0 || limit_cycles > 2000000000ll || code == 0)
+    return refuse(ST_BAD_SIZE, "wait_probe: a flag, a limit of 1..2e9 cycles and a nonzero code");
+  wait_probe_kernel<<<1, 32, 0, stream>>>(err_flag, limit_cycles, code);
+  return launched();
 }
 
 // The width of the token tiles this file's entry point picks for a product of M tokens and N weight

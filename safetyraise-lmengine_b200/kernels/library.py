@@ -233,6 +233,15 @@ class KernelLibrary:
         step's read-back sees it; None goes back to the library's own word."""
         self._bound_err = flag
 
+    def wait_probe(self, flag: torch.Tensor, limit_cycles: int = 1_000_000, code: int = 99) -> None:
+        """A kernel whose one bounded wait (the pipelines' own, on a barrier nobody arrives at) runs out after
+        ``limit_cycles`` and writes ``code`` to flag[0], then ends normally.  For tests of the way from such a
+        wait to the host; the product path never launches it."""
+        if flag.dtype != torch.int32:
+            raise ShapeError("wait_probe: an int32 flag")
+        self._check(self.lib.srlm_wait_probe(_ptr(flag), C.c_longlong(limit_cycles), C.c_int(code), _stream()),
+                    "wait_probe")
+
     def gemm_error_flag(self, device) -> int:
         """Nonzero if a kernel gave up on a bounded wait since the flag was last read (synchronises)."""
         err = self._gemm_state(device)[1]

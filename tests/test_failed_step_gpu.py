@@ -173,3 +173,39 @@ def test_generation_reads_a_fault_word_raised_during_a_prompt_portion(folder_a):
     assert res is not None and res.finish_reason == "error" and "bounded wait" in res.error
     assert llm.engine.cache.free_pages() == 40 and llm.engine.cache.audit() == 0
     assert not llm.step()
+
+
+def test_a_wait_that_runs_out_raises_the_word_and_fails_the_step(folder_a):
+    """A bounded wait that really runs out on the device: the pipelines' own wait, on a barrier that nobody
+    arrives at, with a limit of a million cycles.  The kernel raises the engine's word, ends normally, the
+    step that was on the device with it keeps nothing, and the context goes on working."""
+    from safetyraise_lmengine_b200 import StepEntry
+    from safetyraise_lmengine_b200.errors import ShapeError, StepFailed
+    from safetyraise_lmengine_b200.kernels import ops
+    eng = build(folder_a)
+    rng = np.random.default_rng(9)
+    toks = random_tokens(rng, 19, TINY["A"][0]["vocab_size"])
+    ref = plain_logits(folder_a, toks)
+    s = eng.open_request()
+    eng.step([StepEntry(s, toks[:7], [6])])
+    before = state_of(eng, s)
+    t0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0[0].record()
+    ops.wait_probe(eng.status[:1], limit_cycles=1_000_000, code=77)       # the word a pipeline's wait raises
+    t0[1].record()
+    with pytest.raises(StepFailed, match="bounded wait") as err:
+        eng.step([StepEntry(s, toks[7:16], [8])])
+    assert err.value.words[0] == 77 and sum(1 for w in err.value.words if w) == 1
+    assert 0.1 < t0[0].elapsed_time(t0[1]) < 50.0            # it waited for its limit (about half a millisecond)
+    assert state_of(eng, s) == before
+    assert eng.read_faults() == [0] * 8
+    got = eng.step([StepEntry(s, toks[7:], list(range(12)))]).cpu().numpy()
+    assert np.abs(got - ref[7:]).max() <= TOL["float32"] * np.abs(ref).max()
+    eng.close_request(s)
+    assert eng.cache.free_pages() == 24 and eng.cache.audit() == 0 and eng.steps_failed == 1
+    # the library's own flag, read and cleared by gemm_error_flag
+    ops.bind_error_flag(None)
+    ops.wait_probe(ops._gemm_state(eng.status.device)[1], limit_cycles=200_000, code=5)
+    assert ops.gemm_error_flag(eng.status.device) == 5 and ops.gemm_error_flag(eng.status.device) == 0
+    with pytest.raises(ShapeError):
+        ops.wait_probe(eng.status[:1], limit_cycles=3_000_000_000)        # beyond a second: refused
