@@ -9,8 +9,11 @@
 // the global loads stay 16 bytes wide and whole 32-byte sectors are used.
 //
 // For a handful of tokens the product is bound by HBM alone; what matters is
-// that all SMs stream at once with little fixed cost per launch, which this
-// kernel does better than a TMA/TMEM pipeline sized for hundreds of tokens.
+// that all SMs stream at once with little fixed cost per launch.  The one-tile
+// tcgen05 kernel with 16-token tiles and its K splits in a thread-block cluster
+// (gemm_tcgen05.cu) does that better still (a decode layer's four products at 8
+// tokens: 70.8 against 82.8 us), so this kernel serves no step unless
+// KernelLibrary.skinny_max_tokens is raised; its tests keep it honest.
 // The eight warps' partial sums are added in warp order: the same on every run.
 //
 // Replaces, for decode, the same reference code as gemm_tcgen05.cu

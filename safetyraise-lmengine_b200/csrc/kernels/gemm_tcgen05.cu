@@ -186,7 +186,7 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-// Optional fusions of the one-tile kernel with the norms around a product (decode steps of 9 to 128 tokens;
+// Optional fusions of the one-tile kernel with the norms around a product (steps of 1 to 128 tokens;
 // the same scheme as the weight-streaming kernel's, gemm_skinny.cu):
 //  * scale_parts [n_parts][ld_parts]: the tokens X are (residual * norm weight) in bfloat16, not yet divided
 //    by their RMS; the product is scaled per token by rsqrt(sum_p scale_parts[p][token] / norm_width + eps).
@@ -1460,7 +1460,7 @@ extern "C" int srlm_gemm_tn_tcgen05(const void* X, const void* W, void* C, int c
                     nullptr, stream);
 }
 
-// The same product for 9 to 128 tokens fused with the norms around it (see GemmFuse).  scale_parts may be
+// The same product for 1 to 128 tokens fused with the norms around it (see GemmFuse).  scale_parts may be
 // null (X is already normalised); residual may be null (the product is stored to C, possibly through
 // SwiGLU); with residual C is not written and may be null.
 extern "C" int srlm_gemm_tn_tcgen05_fused(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
