@@ -174,19 +174,20 @@ class LLM:
     def _plan_ahead(self, plan, sampled, states) -> bool:
         """While the device runs a decode step, does the host half of the next one: bookkeeping of this
         step, the scheduler's plan, page reservation and batch layout, with the ids of the tokens being
-        sampled left open.  Only when no token value can change the plan: every entry decodes, nobody
-        waits in the queue, nobody reaches its length.  A stop token still can: then the prepared step
-        is taken back.  Returns whether this step's bookkeeping (advance, append_token) was done."""
-        if not self.config.plan_ahead or len(sampled) != len(plan) or any(p.count != 1 for p in plan):
-            return False
-        if self.scheduler.counters()["queued"]:
+        sampled left open.  Only when no token value can change the plan: nobody reaches its length in
+        this step (whoever waits in the queue is then admitted by the same rule a turn later would apply
+        to the same state).  A stop token still can: then the prepared step is taken back.  Returns
+        whether this step's bookkeeping (advance, append_token) was done."""
+        if not self.config.plan_ahead:
             return False
         for st in states:
             if len(st.tokens) - st.usage.prompt_tokens + 1 >= st.request.sampling.max_new_tokens:
                 return False
+        samples = {p.request_id for p in sampled}
         for p in plan:
             self.scheduler.advance(p.request_id, p.count)
-            self.scheduler.append_token(p.request_id)
+            if p.request_id in samples:
+                self.scheduler.append_token(p.request_id)
         nxt, preempted = self.scheduler.plan()
         for rid in preempted:
             self._live[rid].usage.preemptions += 1
@@ -226,16 +227,16 @@ class LLM:
         for p in plan:
             self.scheduler.rollback(p.request_id)
 
-    def _may_launch_ahead(self, states) -> bool:
+    def _may_launch_ahead(self) -> bool:
         """The step laid out ahead may be queued before this step's tokens are read: its token ids are
         taken on the device, so nothing of it may need them on the host -- no repetition penalty (its
-        history) -- and what a dropped step leaves behind must be what ``Engine.revoke`` restores."""
+        history).  Only decode steps: launching a step with a prompt portion kernel by kernel takes the
+        host milliseconds, by which this step's tokens would reach their readers later."""
         if not self.config.launch_ahead or self._prepared is None:
             return False
-        if any(s.request.sampling.repetition_penalty != 1.0 for s in states):
-            return False
-        nxt, _, later = self._prepared
-        return len(later) == len(nxt)            # every entry decodes the token being sampled now
+        nxt, _, _ = self._prepared
+        return all(p.count == 1 for p in nxt) and \
+            all(self._live[p.request_id].request.sampling.repetition_penalty == 1.0 for p in nxt if p.want_logits)
 
     def _launch_ahead(self, sampled) -> None:
         """Queues the step that was laid out ahead behind this step's sampler: its open token ids are
@@ -249,10 +250,13 @@ class LLM:
             for p in nxt:                              # planned normally at the next turn
                 self.scheduler.rollback(p.request_id)
             return
-        states = [self._live[p.request_id] for p in nxt if p.want_logits]
+        ids = [p.request_id for p in nxt if p.want_logits]
+        states = [self._live[rid] for rid in ids]
+        # a request sampled in the step before has one token more than its list shows yet
         rows = self.sampler.launch(
             logits, [s.request.sampling for s in states], [s.seed for s in states],
-            [len(s.tokens) - s.usage.prompt_tokens + 1 for s in states], [s.tokens for s in states])
+            [len(s.tokens) - s.usage.prompt_tokens + (rid in row_of) for rid, s in zip(ids, states)],
+            [s.tokens for s in states])
         self._inflight = (nxt, prep, rows)
         self.steps_ahead += 1
 
@@ -309,7 +313,7 @@ class LLM:
                 [len(s.tokens) - s.usage.prompt_tokens for s in states], [s.tokens for s in states])
         self.last_step = {"starts": [p.start for p in plan], "counts": [p.count for p in plan]}
         ahead = self._plan_ahead(plan, sampled, states)        # overlaps the device's work
-        if ahead and self._may_launch_ahead(states):
+        if ahead and self._may_launch_ahead():
             rows = self.sampler.snapshot(rows)                 # this step's tokens and words, read below
             self._launch_ahead(sampled)                        # the next step waits on the device already
         tokens = self.sampler.collect(rows)                     # waits for the device; the fault words come along
