@@ -229,14 +229,13 @@ class LLM:
 
     def _may_launch_ahead(self) -> bool:
         """The step laid out ahead may be queued before this step's tokens are read: its token ids are
-        taken on the device, so nothing of it may need them on the host -- no repetition penalty (its
-        history).  Only decode steps: launching a step with a prompt portion kernel by kernel takes the
-        host milliseconds, by which this step's tokens would reach their readers later."""
+        taken on the device, and so is the last id of a repetition penalty's history.  Only decode steps:
+        launching a step with a prompt portion kernel by kernel takes the host milliseconds, by which this
+        step's tokens would reach their readers later."""
         if not self.config.launch_ahead or self._prepared is None:
             return False
         nxt, _, _ = self._prepared
-        return all(p.count == 1 for p in nxt) and \
-            all(self._live[p.request_id].request.sampling.repetition_penalty == 1.0 for p in nxt if p.want_logits)
+        return all(p.count == 1 for p in nxt)
 
     def _launch_ahead(self, sampled) -> None:
         """Queues the step that was laid out ahead behind this step's sampler: its open token ids are
@@ -256,7 +255,7 @@ class LLM:
         rows = self.sampler.launch(
             logits, [s.request.sampling for s in states], [s.seed for s in states],
             [len(s.tokens) - s.usage.prompt_tokens + (rid in row_of) for rid, s in zip(ids, states)],
-            [s.tokens for s in states])
+            [s.tokens for s in states], pending=[row_of.get(rid) for rid in ids])
         self._inflight = (nxt, prep, rows)
         self.steps_ahead += 1
 

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..parts.base import FAULT_LOGITS, STATUS_WORDS
+from ..parts.base import FAULT_LOGITS, FAULT_TOKEN, STATUS_WORDS
 from .params import SamplingParams
 
 _MASK = (1 << 64) - 1
@@ -117,9 +117,13 @@ class Sampler:
         self.last_words = [0] * self._words
 
     def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               indices: Sequence[int], histories: Sequence[Sequence[int]]) -> int:
+               indices: Sequence[int], histories: Sequence[Sequence[int]], pending=None) -> int:
         """Starts the sampling kernel for the rows of ``logits``; returns the number of rows.  The host
-        does not wait: collect() does."""
+        does not wait: collect() does.
+
+        pending: per row, None or the row of the launch before this one whose token (still on the device,
+        behind the fault words) is the last of this row's history: a repetition penalty counts it, the
+        device puts it in place."""
         n = logits.shape[0]
         if n == 0:
             return 0
@@ -147,26 +151,47 @@ class Sampler:
         if any(p.repetition_penalty != 1.0 for p in params):
             # ids and row offsets go through one pinned buffer and one asynchronous copy: a pageable
             # copy would make the host wait for the forward that is still running on the device
-            lens = [len(hh) if p.repetition_penalty != 1.0 else 0 for p, hh in zip(params, histories)]
+            late = [pending is not None and pending[i] is not None and p.repetition_penalty != 1.0
+                    for i, p in enumerate(params)]
+            lens = [len(hh) + late[i] if p.repetition_penalty != 1.0 else 0
+                    for i, (p, hh) in enumerate(zip(params, histories))]
             total = sum(lens)
-            words = n + 1 + max(total, 1)
-            if self._hist_host is None or self._hist_host.numel() < words:
-                cap = max(words, 2 * (self._hist_host.numel() if self._hist_host is not None else 4096))
-                self._hist_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            words = n + 1 + max(total, 1) + 2 * sum(late)            # (the pairs of patch_words ride behind)
+            if self._hist_host is None or self._hist_host[0][0].numel() < words:
+                cap = max(words, 2 * (self._hist_host[0][0].numel() if self._hist_host is not None else 4096))
+                # pinned buffers taken in turn, like the parameters' (a launch may be queued before the copy of
+                # the launch ahead of it has run)
+                self._hist_host = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), None] for _ in range(3)]
                 self._hist_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-            hh_np = self._hist_host.numpy()
+                self._hist_turn = 0
+            self._hist_turn = (self._hist_turn + 1) % len(self._hist_host)
+            hist_pair = self._hist_host[self._hist_turn]
+            if hist_pair[1] is not None:
+                hist_pair[1].synchronize()
+            hh_np = hist_pair[0].numpy()
             hh_np[0] = 0
             np.cumsum(lens, out=hh_np[1:n + 1])
             at = n + 1
-            for ln, hist_ids in zip(lens, histories):
+            pairs = []
+            for i, (ln, hist_ids) in enumerate(zip(lens, histories)):
                 if ln:
-                    hh_np[at:at + ln] = hist_ids
+                    hh_np[at:at + ln - late[i]] = hist_ids
+                    if late[i]:
+                        hh_np[at + ln - 1] = -1                       # an id the kernel skips, until it is put in place
+                        pairs += [at + ln - 1, int(pending[i])]
                     at += ln
             if total == 0:
                 hh_np[n + 1] = 0
-            self._hist_dev[:words].copy_(self._hist_host[:words], non_blocking=True)
+            ids_end = n + 1 + max(total, 1)
+            hh_np[ids_end:ids_end + len(pairs)] = pairs
+            self._hist_dev[:words].copy_(hist_pair[0][:words], non_blocking=True)
+            hist_pair[1] = torch.cuda.Event()
+            hist_pair[1].record()
+            if pairs:
+                ops.patch_words(self._hist_dev, self._hist_dev[ids_end:ids_end + len(pairs)],
+                                self._status[self._words:], len(pairs) // 2, self._status[FAULT_TOKEN:FAULT_TOKEN + 1])
             offs = self._hist_dev[:n + 1]
-            hist = self._hist_dev[n + 1:words]
+            hist = self._hist_dev[n + 1:ids_end]
         if self._scratch is None or self._scratch.shape[0] < self._cap:
             self._scratch = torch.empty(self._cap, self.vocab, dtype=torch.float32, device=self.device)
         ops.sample(logits, d[:n], d[4 * c:4 * c + n].view(torch.int32), d[c:c + n], d[2 * c:2 * c + n],

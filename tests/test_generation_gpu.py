@@ -249,6 +249,40 @@ def test_sampling_kernel_follows_the_plain_sampler(V):
     assert again == got                               # same seed and index: same tokens
 
 
+def test_a_penalty_counts_the_token_that_is_still_on_the_device():
+    """The last id of a row's history may be the token that the launch before this one sampled and that the
+    host has not read yet: the sampler puts it in place on the device (``pending``)."""
+    from safetyraise_lmengine_b200.sampling.sampler import Sampler
+    V, n = 700, 4
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rng = np.random.default_rng(8)
+    last = [int(t) for t in rng.integers(0, V, size=n)]               # what the launch before "sampled"
+    first = torch.full((n, V), -5.0, device="cuda")
+    for i, t in enumerate(last):
+        first[i, t] = 9.0
+    logits = torch.randn(n, V, device="cuda", generator=g) * 3
+    for i, t in enumerate(last):
+        logits[i, t] = logits[i].max() + 0.5                          # the penalty on that id decides the row
+    hist = [[int(t) for t in rng.integers(0, V, size=k)] for k in (5, 0, 17, 3)]
+    params = [SamplingParamsOf(1.5, 0.0), SamplingParamsOf(1.3, 0.8), SamplingParamsOf(1.0, 0.7), SamplingParamsOf(2.0, 0.0)]
+    seeds, idx = [11, 12, 13, 14], [3, 4, 5, 6]
+    whole = Sampler("cuda", V, n).sample(logits, params, seeds, idx, [h + [t] for h, t in zip(hist, last)])
+    s = Sampler("cuda", V, n)
+    s.launch(first, [SamplingParamsOf(1.0, 0.0)] * n, seeds, idx, [[]] * n)          # leaves `last` in the rows
+    got = s.collect(s.launch(logits, params, seeds, idx, hist, pending=[0, 1, 2, 3]))
+    assert got == whole
+    without = Sampler("cuda", V, n).sample(logits, params, seeds, idx, hist)
+    assert without[0] == last[0] != whole[0] and without[3] == last[3] != whole[3]   # it was the penalty's doing
+    # a row that waits for no token keeps its history as given
+    got = s.collect(s.launch(logits, params, seeds, idx, [h + [t] for h, t in zip(hist, last)], pending=[None] * n))
+    assert got == whole
+
+
+def SamplingParamsOf(penalty, temperature):
+    from safetyraise_lmengine_b200 import SamplingParams
+    return SamplingParams(temperature=temperature, repetition_penalty=penalty, top_k=0, top_p=1.0, max_new_tokens=4)
+
+
 @pytest.mark.parametrize("V, n", [(151936, 2), (40000, 30), (9000, 5), (8196, 70), (33000, 148)])
 def test_sampling_rows_shared_by_clusters_of_blocks(V, n):
     """Long rows are shared by a cluster of 8, 4, 2 or 1 blocks, depending on their length and number:
