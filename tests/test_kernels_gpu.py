@@ -886,3 +886,37 @@ def test_gemm_tcgen05_forms_behind_the_switches():
     done = subprocess.run([sys.executable, "-c", _FALLBACK_FORMS], env=env, capture_output=True, text=True,
                           timeout=300)
     assert done.returncode == 0 and "fallback forms agree" in done.stdout, done.stdout[-2000:] + done.stderr[-2000:]
+
+
+def test_products_of_random_sizes_through_the_dispatcher():
+    """Token counts, widths and depths drawn at random (a fixed seed) through ``ops.gemm`` and, up to 128
+    tokens, through the form with the residual and the next norm inside: whatever tile, split and ring the
+    plans pick for a size, the result is the float32 reference's."""
+    import random
+    rnd = random.Random(0)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    done = 0
+    while done < 150:
+        M = rnd.choice([1, 2, 3, 5, 8, 9, 12, 16, 17, 24, 31, 32, 33, 48, 63, 64, 65, 96, 127, 128, 129, 200, 256, 257,
+                        400, 512, 700])
+        N = rnd.choice([8, 16, 24, 96, 100, 128, 136, 264, 1000, 2048, 4096, 5120, 6144, 7168, 9000, 24576])
+        K = 8 * rnd.choice([1, 3, 8, 9, 16, 33, 64, 72, 128, 257, 512, 640, 1024, 1536, 2176])
+        if M * N > 6e6 or N * K > 7e7:
+            continue
+        done += 1
+        a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.float32)
+        ops().gemm(a, w, out)
+        ref = a.float() @ w.float().T
+        assert torch.allclose(out, ref, rtol=1e-4, atol=2e-4 * math.sqrt(K)), (M, N, K)
+        if M <= 128 and N % 8 == 0:
+            res = torch.randn(M, N, device=DEV, generator=g)
+            got = res.clone()
+            xw = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+            ss = torch.zeros((N + 127) // 128, 128, device=DEV)
+            ops().gemm_tn_tcgen05_fused(a, w, residual=got, next_w=torch.ones(N, device=DEV), xw_out=xw, ss_out=ss)
+            want = res.double() + a.double() @ w.double().T
+            assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-3), (M, N, K)
+            assert torch.allclose(ss[:, :M].sum(0).double(), (want ** 2).sum(-1), rtol=1e-4, atol=1e-4), (M, N, K)
+    assert ops().gemm_error_flag(torch.device(DEV)) == 0
