@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 from conftest import TINY
-from helpers import (TOL, check_against_plain, cut_bulk_tail, cut_portions, cut_whole, plain_logits,
+from helpers import (TOL, check_against_plain, cut_bulk_tail, cut_portions, cut_whole, note_error, plain_logits,
                      random_tokens, rel_err, replay)
 
 pytestmark = pytest.mark.gpu
@@ -419,3 +419,51 @@ def test_norms_fused_into_products_of_up_to_128_tokens(name, tmp_path_factory):
         ref = plain_logits(folder, t[:35])
         for p in [22, 26] + list(range(27, 35)):
             assert np.abs(out[True][(r, p)] - ref[p]).max() <= TOL["bfloat16"] * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["F", "G"])
+def test_schedules_drawn_at_random_agree_with_plain(name, dtype, tmp_path_factory):
+    """Up to four live requests fed in portions and single tokens of random sizes, some sitting a step out,
+    with as few pages as the four longest need: every asked place against the plain logits (fixed seeds)."""
+    from conftest import make_folder
+    from safetyraise_lmengine_b200 import Engine
+    cfg, wseed = TINY[name]
+    folder = make_folder(tmp_path_factory, cfg, wseed, "sched_" + name.lower())
+    for trial in range(4):
+        rng = np.random.default_rng(100 + trial)
+        ps = int(rng.choice([4, 16]))
+        maxlen = min(cfg["max_position_embeddings"], 140)
+        reqs = {f"r{i}": random_tokens(rng, int(rng.integers(2, maxlen)), cfg["vocab_size"])
+                for i in range(int(rng.integers(3, 9)))}
+        pages = sorted(((len(t) + ps - 1) // ps for t in reqs.values()), reverse=True)
+        num_pages = sum(pages[:4]) + 1
+        eng = Engine.from_folder(folder, dtype=dtype, page_size=ps, num_pages=num_pages, max_requests=4,
+                                 max_batch_tokens=512)
+        waiting, live, fed, steps = list(reqs), [], {}, []
+        while waiting or live:
+            while waiting and len(live) < 4 and rng.random() < 0.7:
+                live.append(waiting.pop(0))
+                fed[live[-1]] = 0
+            entries, ends = [], []
+            for r in list(live):
+                if rng.random() < 0.25 and len(live) > 1:
+                    continue                                  # sits this step out
+                left = len(reqs[r]) - fed[r]
+                n = 1 if rng.random() < 0.5 else int(rng.integers(1, min(left, 40) + 1))
+                want = sorted(set(int(x) for x in rng.integers(0, n, size=int(rng.integers(0, min(n, 3) + 1)))))
+                entries.append((r, reqs[r][fed[r]:fed[r] + n], want))
+                fed[r] += n
+                if fed[r] == len(reqs[r]):
+                    ends.append(r)
+                    live.remove(r)
+            if entries:
+                steps.append({"entries": entries, "end": ends})
+        got = replay(eng, steps)
+        assert got
+        for (r, pos), row in got.items():
+            ref = plain_logits(folder, reqs[r])
+            err = float(np.abs(row - ref[pos]).max() / np.abs(ref).max())
+            note_error(dtype, err, f"random schedule {name}")
+            assert err <= TOL[dtype], (trial, r, pos, err)
+        assert eng.cache.audit() == 0 and eng.cache.free_pages() == num_pages
