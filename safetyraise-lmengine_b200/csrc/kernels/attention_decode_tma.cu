@@ -234,15 +234,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   // themselves, so it may still be running.
   const bool ahead_of_wait = (HD == 64 || HD == 128 || HD == 256) && a.qkv != nullptr && a.write_kv &&
                              warp == CONSUMERS;
-  if (!ahead_of_wait) {
-    pdl_wait();
-    pdl_trigger();
-  }
+  // (the batch's layout is read ahead of the wait by every warp: it was copied before the step's first kernel)
   const int e = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z;
   const int g = a.nq / a.nkv;
   const int q0 = a.cu_q[e], q_len = a.cu_q[e + 1] - q0, kv_len = a.kv_lens[e], start = kv_len - q_len;
   const int rows_total = q_len * g;
   const int* table = a.block_table + (size_t)e * a.table_stride;
+  if (!ahead_of_wait) {
+    pdl_wait();
+    pdl_trigger();
+  }
 
   const int first_key = a.window > 0 ? max(0, start - a.window + 1) : 0;
   const int slice_lo = z * a.kv_chunk, slice_hi = min(kv_len, slice_lo + a.kv_chunk);
