@@ -232,8 +232,8 @@ class LLM:
         taken on the device, and so is the last id of a repetition penalty's history.  Only decode steps:
         launching a step with a prompt portion kernel by kernel takes the host milliseconds, by which this
         step's tokens would reach their readers later."""
-        if not self.config.launch_ahead or self._prepared is None:
-            return False
+        if not self.config.launch_ahead or self._prepared is None or not self.engine.use_graphs:
+            return False                 # (without graphs a decode step is launched kernel by kernel too)
         nxt, _, _ = self._prepared
         return all(p.count == 1 for p in nxt)
 
