@@ -301,6 +301,10 @@ class KernelLibrary:
                 # 8B sizes: 36.1 -> 31.3 us with 4 instead of 3 (64 tiles); 512 tokens, 8B: 58.4 -> 51.8 us
                 # with 2 splits of 128 tiles
                 sp = min(256 // max(1, tiles), total_kb // 8, 4)
+                if M <= 128:
+                    # one token tile: a long K pays more splits (down projection of 128 tokens, 4096 x 12,288:
+                    # 28.5 us in 4 splits, 25.6 in 6, 24.3 in 8; the output projection's K of 4096 does not)
+                    sp = max(sp, min(256 // max(1, tiles), total_kb // 16, 8))
             sp = max(1, sp)
             if M <= 64 and sp == 1 and 148 < tiles and 2 * tiles <= 444 and total_kb >= 16:
                 sp = 2        # three blocks of a shallower ring an SM (the kernel picks it by the block count)
